@@ -6,6 +6,7 @@ from .manager import (
     OutOfPages,
     PagePool,
     RequestCache,
+    StepMemories,
 )
 
 __all__ = [
@@ -16,4 +17,5 @@ __all__ = [
     "OutOfPages",
     "PagePool",
     "RequestCache",
+    "StepMemories",
 ]

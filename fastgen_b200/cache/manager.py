@@ -118,6 +118,14 @@ class LayerMemory:
     layer_index: int = 0  # this run's index within the group's pools
 
 
+class StepMemories(list):
+    """What a forward pass is handed: the :class:`LayerMemory` of every schedule entry (the
+    list's items) and ``embedder_state``, the per-request state of an embedder that keeps one
+    (``[n_slots, *shape]``, or ``None``)."""
+
+    embedder_state: Optional[torch.Tensor] = None
+
+
 class RequestCache:
     """A live request's holdings: its slot, its length and its pages per group."""
 
@@ -159,6 +167,7 @@ class CacheManager:
         dtype: torch.dtype = torch.float32,
         device=None,
         tensor_map_factory=None,
+        embedder_state: Optional[StateSpec] = None,
     ) -> None:
         if page_size <= 0:
             raise ValueError(f"page size must be positive, got {page_size}")
@@ -212,6 +221,7 @@ class CacheManager:
 
         self.state_specs = list(state_specs)
         self.states: List[Optional[torch.Tensor]] = [None] * n_entries
+        self.embedder_state: Optional[torch.Tensor] = None  # the embedder's state, [slots, *shape]
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._requests: Dict[object, RequestCache] = {}
 
@@ -235,8 +245,12 @@ class CacheManager:
             for e, st in enumerate(self.state_specs):
                 if st is not None:
                     self.states[e] = torch.zeros(
-                        (max_requests, *st.shape), dtype=torch.float32, device=device
+                        (max_requests, *st.shape), dtype=st.dtype, device=device
                     )
+            if embedder_state is not None:
+                self.embedder_state = torch.zeros(
+                    (max_requests, *embedder_state.shape), dtype=embedder_state.dtype, device=device
+                )
 
     # -- queries -------------------------------------------------------------------
     @property
@@ -288,7 +302,7 @@ class CacheManager:
         slot = self._free_slots.pop()
         req = RequestCache(request_id, slot, len(self.groups))
         self._requests[request_id] = req
-        for st in self.states:
+        for st in (*self.states, self.embedder_state):
             if st is not None:
                 st[slot].zero_()
         return req
@@ -371,6 +385,12 @@ class CacheManager:
             val = torch.from_numpy(vals[keep]).to(self.device, non_blocking=False)
             grp.device_table.view(-1).index_copy_(0, idx, val)
             grp.dirty.clear()
+
+    def memories(self) -> StepMemories:
+        """What the model's forward pass needs: every entry's memory and the embedder's state."""
+        out = StepMemories(self.memory(e) for e in range(len(self.entry_group)))
+        out.embedder_state = self.embedder_state
+        return out
 
     def memory(self, entry: int) -> LayerMemory:
         """The :class:`LayerMemory` of schedule entry ``entry``."""

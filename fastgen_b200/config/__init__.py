@@ -13,6 +13,7 @@ from .registry import (
     register_architecture,
 )
 from . import llama as _llama  # registers LlamaForCausalLM
+from . import sinorax as _sinorax  # registers Sinorax
 
 __all__ = [
     "ConfigError",

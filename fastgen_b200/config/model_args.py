@@ -51,8 +51,8 @@ class LayerSpec:
     block: str
     mixer: PartSpec
     mixer_norm: PartSpec
-    ffn: PartSpec
-    ffn_norm: PartSpec
+    ffn: Optional[PartSpec]  # None: a layer without a feed-forward (and without its norm)
+    ffn_norm: Optional[PartSpec]
     extra: Tuple[Tuple[str, str, PartSpec], ...] = ()
 
 
@@ -82,6 +82,15 @@ class ModelArgs:
     schedule: Sequence[ScheduleEntry]
     final_norm: PartSpec
     stop_tokens: Sequence[int] = ()
+    #: how token ids become the first residual stream (``None``: a plain table named
+    #: ``embedding_name``); its ``"table"`` tensor is what a tied output projection uses
+    embedder: Optional[PartSpec] = None
+    #: logits are multiplied by ``logit_scale`` and then, with a cap, squashed to
+    #: ``cap * tanh(logits / cap)``
+    logit_scale: float = 1.0
+    logit_softcap: Optional[float] = None
+    #: tensors a checkpoint may hold without the model using them
+    optional_tensors: Sequence[str] = ()
 
     def __post_init__(self) -> None:
         n = len(self.layers)

@@ -30,10 +30,12 @@ def architectures() -> list[str]:
 def model_args_from_config(config: Mapping[str, Any]) -> ModelArgs:
     """Turn a parsed ``config.json`` into a :class:`ModelArgs`."""
     archs = config.get("architectures")
+    if archs is None and isinstance(config.get("architecture"), str):
+        archs = [config["architecture"]]  # some configurations name theirs in the singular
     if not isinstance(archs, (list, tuple)) or len(archs) != 1:
         raise ConfigError(
             "config.json must name exactly one architecture under "
-            f"'architectures', got {archs!r}"
+            f"'architectures' (or 'architecture'), got {archs!r}"
         )
     name = archs[0]
     builder = _ARCHITECTURES.get(name)

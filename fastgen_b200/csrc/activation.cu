@@ -1,0 +1,90 @@
+// Elementwise pieces around the products:
+//  * fg_bias_act: x[t, f] = act(x[t, f] + bias[f]) in place, for a dense feed-forward
+//    down(act(up x)); act is the exact (erf) GELU, the tanh GELU
+//    0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), or nothing (bias only).  Float32
+//    arithmetic, one rounding.
+//  * fg_scale_softcap: logits[r, v] = cap * tanh(logits[r, v] * scale / cap) in place (float32);
+//    cap <= 0 leaves the scaling alone.
+#include "common.cuh"
+
+namespace {
+
+enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2 };
+
+__device__ __forceinline__ float activate(float z, int act) {
+  if (act == ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+  if (act == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+
+template <typename T>
+__global__ void bias_act_kernel(T* x, const T* __restrict__ bias, int width, size_t total, int act) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    float v = to_f32<T>(x[i]);
+    if (bias != nullptr) v = to_f32<T>(from_f32<T>(v + to_f32<T>(bias[i % width])));
+    x[i] = from_f32<T>(activate(v, act));
+  }
+}
+
+// bfloat16 rows whose width is a multiple of 8, no bias: eight elements (16 bytes) a thread
+__global__ void __launch_bounds__(256) act_bf16x8_kernel(uint4* x, size_t pieces, int act) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < pieces; i += stride) {
+    uint4 raw = x[i];
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 v = __bfloat1622float2(h2[k]);
+      h2[k] = __floats2bfloat162_rn(activate(v.x, act), activate(v.y, act));
+    }
+    x[i] = raw;
+  }
+}
+
+__global__ void scale_softcap_kernel(float* x, size_t total, float scale, float cap) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    x[i] = v;
+  }
+}
+
+int grid_for(size_t items, int threads) {
+  size_t blocks = (items + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return (int)blocks;
+}
+
+}  // namespace
+
+extern "C" int fg_bias_act(void* x, const void* bias, int dtype, int n_rows, int width, int act, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * width;
+  if (total == 0) return 0;
+  FG_CHECK_ARG(act >= ACT_NONE && act <= ACT_GELU_TANH, "fg_bias_act: unknown activation %d", act);
+  const int threads = 256;
+  if (dtype == FG_BF16 && bias == nullptr && total % 8 == 0 && ((uintptr_t)x & 15) == 0)
+    act_bf16x8_kernel<<<grid_for(total / 8, threads), threads, 0, stream>>>((uint4*)x, total / 8, act);
+  else if (dtype == FG_BF16)
+    bias_act_kernel<__nv_bfloat16><<<grid_for(total, threads), threads, 0, stream>>>(
+        (__nv_bfloat16*)x, (const __nv_bfloat16*)bias, width, total, act);
+  else if (dtype == FG_F32)
+    bias_act_kernel<float><<<grid_for(total, threads), threads, 0, stream>>>((float*)x, (const float*)bias, width,
+                                                                            total, act);
+  else
+    FG_CHECK_ARG(false, "fg_bias_act: bad dtype %d", dtype);
+  FG_CHECK_LAUNCH("fg_bias_act");
+  return 0;
+}
+
+extern "C" int fg_scale_softcap(float* x, int n_rows, int width, float scale, float cap, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * width;
+  if (total == 0) return 0;
+  scale_softcap_kernel<<<grid_for(total, 256), 256, 0, stream>>>(x, total, scale, cap);
+  FG_CHECK_LAUNCH("fg_scale_softcap");
+  return 0;
+}

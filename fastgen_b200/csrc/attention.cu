@@ -60,6 +60,54 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
   return 0;
 }
 
+#include "attention_sigmoid.cuh"
+
+// Sigmoid-weighted attention (see attention_sigmoid.cuh); gate, r1 and r2 are float32 [n_heads]
+// or null (r1 and r2 both or neither).  Same tiling contract as fg_attention_simt.
+extern "C" int fg_attention_sigmoid(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                    const void* k_pages, const void* v_pages, const int* block_table,
+                                    int table_width, int page_size, int n_pages, const int* pos,
+                                    const int* tile_req, const int* tile_tok0, const int* tile_ntok,
+                                    int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
+                                    float scale, const float* gate, const float* r1, const float* r2,
+                                    int* status, cudaStream_t stream) {
+  using namespace fg_attn;
+  if (n_tiles == 0) return 0;
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_sigmoid: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0, "fg_attention_sigmoid: %d heads over %d kv heads",
+               n_heads, n_kv_heads);
+  FG_CHECK_ARG(n_kv_heads <= 65535, "fg_attention_sigmoid: too many kv heads");
+  FG_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "fg_attention_sigmoid: r1 and r2 come together");
+  const int group = n_heads / n_kv_heads;
+  const int hpb = group < ROWS ? group : ROWS;
+  dim3 grid(n_tiles, n_kv_heads, (group + hpb - 1) / hpb);
+  constexpr size_t smem = simt_smem_bytes<FG_HEAD_DIM>();
+  cudaError_t e;
+  if (dtype == FG_F32) {
+    auto kern = attention_sigmoid_kernel<float, FG_HEAD_DIM>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_sigmoid: shared memory: %s", cudaGetErrorString(e));
+    kern<<<grid, THREADS, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
+                                          (const float*)k_pages, (const float*)v_pages, block_table,
+                                          table_width, page_size, n_pages, pos, tile_req, tile_tok0,
+                                          tile_ntok, n_kv_heads, group, hpb, window, scale, gate, r1, r2, status);
+  } else if (dtype == FG_BF16) {
+    auto kern = attention_sigmoid_kernel<__nv_bfloat16, FG_HEAD_DIM>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_sigmoid: shared memory: %s", cudaGetErrorString(e));
+    kern<<<grid, THREADS, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_width,
+        page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_kv_heads, group, hpb, window, scale,
+        gate, r1, r2, status);
+  } else {
+    FG_CHECK_ARG(false, "fg_attention_sigmoid: bad dtype %d", dtype);
+  }
+  FG_CHECK_LAUNCH("fg_attention_sigmoid");
+  return 0;
+}
+
 // ---------------------------------------------------------------------------------
 // bfloat16 on the tensor cores
 // ---------------------------------------------------------------------------------

@@ -1,0 +1,169 @@
+// Paged attention with sigmoid weights on the CUDA cores, float32 arithmetic throughout.
+//
+//   out[i, h] = sum over visible j of  sigmoid(q_i . k_j * scale + gate[h] - r1[h] * ln(1 + r2[h] * (i - j))) * v_j
+//
+// The weight of a key is a sigmoid of its own score: nothing is normalised over the keys, so
+// there is no running maximum, no rescaling and no division at the end.  gate is a number per
+// query head added to the score; r1 and r2 (per head, both or neither) give a logarithmic
+// distance bias that is taken off the score.  A key is visible if j <= i and, with a window,
+// i - j < window.  Grouped-query heads h -> h / (Hq/Hkv).
+//
+// Tiling, paging and the order of the sums are those of attention_simt_kernel: a block takes
+// one tile of query tokens for one group of heads, keys come from the cache pages in tiles of
+// 32 positions that start at multiples of 32, and a key that is not visible adds an exact zero,
+// so a row's result does not depend on how the prompt was cut or what else is in the batch.
+//
+// Storage type T (float or bf16) only affects loads and the final store.
+#pragma once
+
+#include "attention_simt.cuh"
+
+namespace fg_attn {
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(THREADS)
+attention_sigmoid_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                         const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                         const int* __restrict__ block_table, int table_width, int page_size,
+                         int n_pages, const int* __restrict__ pos, const int* __restrict__ tile_req,
+                         const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
+                         int n_kv_heads, int group, int heads_per_block, int window, float scale,
+                         const float* __restrict__ gate, const float* __restrict__ r1,
+                         const float* __restrict__ r2, int* status) {
+  constexpr int HP = HD + 1;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float(*Qs)[HP] = reinterpret_cast<float(*)[HP]>(smem_raw);
+  float(*Ks)[HP] = reinterpret_cast<float(*)[HP]>(Qs + ROWS);
+  float(*Vs)[HP] = reinterpret_cast<float(*)[HP]>(Ks + KEYS);
+  float(*Ps)[KEYS + 1] = reinterpret_cast<float(*)[KEYS + 1]>(Vs + KEYS);
+  __shared__ long long key_base[KEYS];
+  __shared__ int row_pos[ROWS];
+
+  const int tile = blockIdx.x;
+  const int g = blockIdx.y;        // key/value head
+  const int sub = blockIdx.z;      // which slice of the group's heads
+  const int b = tile_req[tile];
+  const int tok0 = tile_tok0[tile];
+  const int ntok = tile_ntok[tile];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+
+  auto row_token = [&](int r) { return r / heads_per_block; };
+  auto row_head = [&](int r) { return sub * heads_per_block + (r % heads_per_block); };
+  auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
+
+  if (b < 0) {
+    for (int i = tid; i < ROWS * HD; i += THREADS) {
+      const int r = i / HD, d = i - r * HD;
+      if (row_valid(r))
+        out[(size_t)(tok0 + row_token(r)) * out_stride + (g * group + row_head(r)) * HD + d] = from_f32<T>(0.f);
+    }
+    return;
+  }
+  if (tid < ROWS) row_pos[tid] = row_valid(tid) ? pos[tok0 + row_token(tid)] : -1;
+  for (int i = tid; i < ROWS * HD; i += THREADS) {
+    const int r = i / HD, d = i - r * HD;
+    float v = 0.f;
+    if (row_valid(r))
+      v = to_f32<T>(q[(size_t)(tok0 + row_token(r)) * q_stride + (g * group + row_head(r)) * HD + d]);
+    Qs[r][d] = v;
+  }
+  __syncthreads();
+
+  int max_pos = -1, min_pos = 0x7fffffff;
+  for (int r = 0; r < ROWS; ++r) {
+    const int p = row_pos[r];
+    if (p >= 0) {
+      max_pos = max(max_pos, p);
+      min_pos = min(min_pos, p);
+    }
+  }
+  if (max_pos < 0) return;
+  int k_lo = 0;
+  if (window > 0) k_lo = max(0, min_pos - window + 1) / KEYS * KEYS;
+
+  // this thread's 4 score rows: warp, warp+4, warp+8, warp+12; column = lane.  Their heads' numbers:
+  float g_row[4], r1_row[4], r2_row[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = warp + 4 * i;
+    const int h = g * group + min(row_head(r), group - 1);
+    g_row[i] = gate != nullptr ? gate[h] : 0.f;
+    r1_row[i] = r1 != nullptr ? r1[h] : 0.f;
+    r2_row[i] = r2 != nullptr ? r2[h] : 0.f;
+  }
+  constexpr int OD = HD / 8;
+  float o_acc[OD];
+#pragma unroll
+  for (int i = 0; i < OD; ++i) o_acc[i] = 0.f;
+  const int o_row = tid >> 3, o_col = tid & 7;
+
+  for (int k0 = k_lo; k0 <= max_pos; k0 += KEYS) {
+    if (tid < KEYS) {
+      const int j = k0 + tid;
+      long long base = -1;
+      if (j <= max_pos) {
+        const int logical = j / page_size;
+        const int page = logical < table_width ? block_table[(size_t)b * table_width + logical] : -1;
+        if (page >= 0 && page < n_pages) {
+          base = (((long long)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
+        } else if (window <= 0 || j > min_pos - window) {
+          if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
+        }
+      }
+      key_base[tid] = base;
+    }
+    __syncthreads();
+    for (int i = tid; i < KEYS * HD; i += THREADS) {
+      const int c = i / HD, d = i - c * HD;
+      const long long base = key_base[c];
+      float kv = 0.f, vv = 0.f;
+      if (base >= 0) {
+        kv = to_f32<T>(k_pages[base + d]);
+        vv = to_f32<T>(v_pages[base + d]);
+      }
+      Ks[c][d] = kv;
+      Vs[c][d] = vv;
+    }
+    __syncthreads();
+
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+    for (int d = 0; d < HD; ++d) {
+      const float kv = Ks[lane][d];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i] = fmaf(Qs[warp + 4 * i][d], kv, s[i]);
+    }
+    const int j = k0 + lane;
+    const bool has_key = key_base[lane] >= 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = warp + 4 * i;
+      const int p = row_pos[r];
+      const bool visible = has_key && p >= 0 && j <= p && (window <= 0 || j > p - window);
+      float pr = 0.f;
+      if (visible) {
+        float z = s[i] * scale + g_row[i];
+        if (r1 != nullptr) z -= r1_row[i] * logf(1.f + r2_row[i] * (float)(p - j));
+        pr = 1.f / (1.f + expf(-z));
+      }
+      Ps[r][lane] = pr;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int c = 0; c < KEYS; ++c) {
+      const float pr = Ps[o_row][c];
+#pragma unroll
+      for (int i = 0; i < OD; ++i) o_acc[i] = fmaf(pr, Vs[c][o_col + 8 * i], o_acc[i]);
+    }
+    __syncthreads();
+  }
+
+  if (row_valid(o_row)) {
+    T* o = out + (size_t)(tok0 + row_token(o_row)) * out_stride + (g * group + row_head(o_row)) * HD;
+#pragma unroll
+    for (int i = 0; i < OD; ++i) o[o_col + 8 * i] = from_f32<T>(o_acc[i]);
+  }
+}
+
+}  // namespace fg_attn

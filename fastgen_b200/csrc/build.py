@@ -39,6 +39,8 @@ CORE_SOURCES = [
     "errors.cu",
     "embedding.cu",
     "rmsnorm.cu",
+    "dyt.cu",
+    "activation.cu",
     "rope_kv.cu",
     "silu_gate.cu",
     "gemm_f32.cu",

@@ -5,7 +5,7 @@
 // over k = 0 .. K-1 in ascending order in a single accumulator, so its value
 // does not depend on M, on the tile it falls in, or on what else is in the batch.
 // It stands where the reference calls F.linear (fastgen/forward.py:438-440,470,
-// 491-496,513).
+// 491-496,513).  A bias [N], if given, is added to the finished sum.
 #include "common.cuh"
 
 namespace {
@@ -13,7 +13,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 ou
 
 __global__ void __launch_bounds__(256)
 gemm_f32_nt_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
-                   float* __restrict__ C, int ldc, int M, int N, int K) {
+                   float* __restrict__ C, int ldc, int M, int N, int K, const float* __restrict__ bias) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -58,19 +58,19 @@ gemm_f32_nt_kernel(const float* __restrict__ A, int lda, const float* __restrict
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
-      if (n < N) C[(size_t)m * ldc + n] = acc[i][j];
+      if (n < N) C[(size_t)m * ldc + n] = bias != nullptr ? acc[i][j] + bias[n] : acc[i][j];
     }
   }
 }
 }  // namespace
 
 extern "C" int fg_gemm_f32_nt(const float* A, int lda, const float* W, int ldw, float* C, int ldc,
-                              int M, int N, int K, cudaStream_t stream) {
+                              int M, int N, int K, const float* bias, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   FG_CHECK_ARG(K > 0 && lda >= K && ldw >= K && ldc >= N, "fg_gemm_f32_nt: bad sizes M=%d N=%d K=%d", M, N, K);
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   FG_CHECK_ARG(grid.y <= 65535, "fg_gemm_f32_nt: M=%d too large", M);
-  gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
+  gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K, bias);
   FG_CHECK_LAUNCH("fg_gemm_f32_nt");
   return 0;
 }

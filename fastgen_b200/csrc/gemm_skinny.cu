@@ -36,7 +36,21 @@ constexpr int THREADS = WARPS * 32;
 
 enum { EPI_PLAIN = 0, EPI_QKV = 1, EPI_SWIGLU = 2 };
 
+enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2 };
+
+__device__ __forceinline__ float activate(float z, int act) {
+  if (act == ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+  if (act == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+
+// What the epilogues may need beyond the sums: a bias over the output rows (all epilogues) and
+// an activation (plain epilogue), and for the fused query/key/value projection the positions,
+// tables and pages.
 struct QkvEpilogue {
+  const __nv_bfloat16* bias;  // [N] or null
+  int act;
+  const float* v_freqs;  // [head_dim / 2] or null: values are rotated by their own position too
   const int* pos;
   const int* req;
   const float* freqs;  // [head_dim / 2] or null
@@ -217,10 +231,17 @@ __device__ __forceinline__ float block_total(float (*red)[ROWS][NT * 8], int row
 }
 
 template <int NT, typename TO>
-__device__ __forceinline__ void epilogue_plain(float (*red)[ROWS][NT * 8], TO* y, int ldy, int M, int N, int n0) {
+__device__ __forceinline__ void epilogue_plain(float (*red)[ROWS][NT * 8], TO* y, int ldy, int M, int N, int n0,
+                                               const __nv_bfloat16* bias, int act) {
   for (int i = threadIdx.x; i < ROWS * NT * 8; i += THREADS) {
     const int tok = i / ROWS, row = i - tok * ROWS;  // consecutive threads write consecutive columns of y
-    if (tok < M && n0 + row < N) y[(size_t)tok * ldy + n0 + row] = from_f32<TO>(block_total<NT>(red, row, tok));
+    if (tok < M && n0 + row < N) {
+      float v = block_total<NT>(red, row, tok);
+      if (bias != nullptr) v += __bfloat162float(bias[n0 + row]);
+      // the product is rounded to bfloat16 before the activation, as a separate kernel would see it
+      if (act != ACT_NONE) v = activate(__bfloat162float(__float2bfloat16_rn(v)), act);
+      y[(size_t)tok * ldy + n0 + row] = from_f32<TO>(v);
+    }
   }
 }
 
@@ -269,6 +290,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
       const int p = qkv.pos[tok];
       e_kind = n < q_width ? 0 : (n < q_width + kv_width ? 1 : 2);
       if (e_kind != 2 && qkv.freqs != nullptr) sincosf((float)p * qkv.freqs[(n % hd) >> 1], &e_sin, &e_cos);
+      if (e_kind == 2 && qkv.v_freqs != nullptr) sincosf((float)p * qkv.v_freqs[(n % hd) >> 1], &e_sin, &e_cos);
       e_tok = tok;
       e_n = n;
       if (e_kind != 0) {
@@ -289,7 +311,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
   pdl_wait();
   block.run(red);
   if (EPI == EPI_PLAIN) {
-    epilogue_plain<NT, TO>(red, y, ldy, M, N, n0);
+    epilogue_plain<NT, TO>(red, y, ldy, M, N, n0, qkv.bias, qkv.act);
   } else if (EPI == EPI_SWIGLU) {
     epilogue_swiglu<NT, TO>(red, y, ldy, M, N, n0);
   } else {
@@ -298,7 +320,11 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
     if (e_tok >= 0) {
       const int pr = (e_n - n0) >> 1;
       float re = block_total<NT>(red, 2 * pr, e_tok), im = block_total<NT>(red, 2 * pr + 1, e_tok);
-      if (e_kind != 2) {
+      if (qkv.bias != nullptr) {
+        re += __bfloat162float(qkv.bias[e_n]);
+        im += __bfloat162float(qkv.bias[e_n + 1]);
+      }
+      if (e_kind != 2 || qkv.v_freqs != nullptr) {
         // the product is rounded to bfloat16 before the rotation, as a separate kernel would see it
         re = __bfloat162float(__float2bfloat16_rn(re));
         im = __bfloat162float(__float2bfloat16_rn(im));
@@ -371,11 +397,16 @@ extern "C" int fg_gemm_skinny_max_m() { return 32; }
 
 // x: [M, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), y: [M, N] bf16 or
 // float32.  Needs M <= 32, K % 8 == 0, 16-byte aligned x and w with strides % 8 == 0.
+// bias: bf16 [N] or null, added to the sums; act: ACT_* applied after it.
 extern "C" int fg_gemm_skinny_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
-                                   int out_dtype, int M, int N, int K, cudaStream_t stream) {
+                                   int out_dtype, int M, int N, int K, const void* bias, int act,
+                                   cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (check_common("fg_gemm_skinny_bf16", x, ldx, w, ldw, ldy, M, N, K, K)) return -1;
+  FG_CHECK_ARG(act >= ACT_NONE && act <= ACT_GELU_TANH, "fg_gemm_skinny_bf16: unknown activation %d", act);
   QkvEpilogue none{};
+  none.bias = (const __nv_bfloat16*)bias;
+  none.act = act;
   if (out_dtype == FG_BF16)
     launch<__nv_bfloat16, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
   else if (out_dtype == FG_F32)
@@ -402,12 +433,14 @@ extern "C" int fg_gemm_skinny_swiglu_bf16(const void* x, int ldx, const void* w,
 // The fused projection of queries, keys and values for single tokens and small
 // batches: w = [wq; wk; wv] with N = (n_heads + 2 n_kv_heads) * head_dim.  Rotated
 // queries go to y[:, :n_heads*head_dim]; rotated keys and the values go to the
-// pages of (req[t], pos[t]).  freqs may be null (no rotation).
+// pages of (req[t], pos[t]).  freqs may be null (no rotation); v_freqs, if given, turns the
+// values by their own position as well; bias (bf16 [N], or null) is added before the rounding.
 extern "C" int fg_gemm_skinny_qkv_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
-                                       int M, int K, const int* pos, const int* req, const float* freqs,
-                                       void* k_pages, void* v_pages, const int* block_table, int table_width,
-                                       int page_size, int n_pages, int n_heads, int n_kv_heads, int head_dim,
-                                       int* status, cudaStream_t stream) {
+                                       int M, int K, const void* bias, const int* pos, const int* req,
+                                       const float* freqs, const float* v_freqs, void* k_pages, void* v_pages,
+                                       const int* block_table, int table_width, int page_size, int n_pages,
+                                       int n_heads, int n_kv_heads, int head_dim, int* status,
+                                       cudaStream_t stream) {
   const int N = (n_heads + 2 * n_kv_heads) * head_dim;
   if (M == 0) return 0;
   if (check_common("fg_gemm_skinny_qkv_bf16", x, ldx, w, ldw, ldy, M, n_heads * head_dim, K, K)) return -1;
@@ -415,7 +448,7 @@ extern "C" int fg_gemm_skinny_qkv_bf16(const void* x, int ldx, const void* w, in
   FG_CHECK_ARG(ldy % 2 == 0 && ((uintptr_t)y & 3) == 0 && ((uintptr_t)k_pages & 3) == 0 &&
                    ((uintptr_t)v_pages & 3) == 0,
                "fg_gemm_skinny_qkv_bf16: outputs must be 4-byte aligned");
-  QkvEpilogue qkv{pos, req, freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width,
+  QkvEpilogue qkv{(const __nv_bfloat16*)bias, ACT_NONE, v_freqs, pos, req, freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width,
                   page_size, n_pages, n_heads, n_kv_heads, head_dim, status};
   launch<__nv_bfloat16, EPI_QKV>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
   FG_CHECK_LAUNCH("fg_gemm_skinny_qkv_bf16");

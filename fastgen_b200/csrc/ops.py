@@ -44,12 +44,16 @@ _CORE_SIGNATURES = {
     "fg_embedding": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     "fg_rmsnorm": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P],
     "fg_silu_gate": [_P, _P, _I, _I, _I, _I, _P],
-    "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "fg_gemm_f32_nt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
-    "fg_gemm_skinny_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+    "fg_embedding_bigram": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fg_dyt": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P],
+    "fg_bias_act": [_P, _P, _I, _I, _I, _I, _P],
+    "fg_scale_softcap": [_P, _I, _I, _F, _F, _P],
+    "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fg_gemm_f32_nt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _P],
+    "fg_gemm_skinny_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _I, _P],
     "fg_gemm_skinny_swiglu_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
-    "fg_gemm_skinny_qkv_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
-                                _P, _P],
+    "fg_gemm_skinny_qkv_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
+                                _I, _I, _P, _P],
     "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P, _P],
     "fg_selftest_wait_timeout": [_I, _P, _P, _P],
     "fg_sample_uniform": [c_ulonglong, _P, _P, _P, _I, _P],
@@ -58,6 +62,8 @@ _CORE_SIGNATURES = {
 
 _ATTN_SIGNATURES = {
     "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "fg_attention_sigmoid": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
+                             _P, _P, _P, _P, _P],
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
                                  ctypes.c_longlong, _I, _P, _P],
@@ -77,6 +83,9 @@ PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
 PREFILL_TMA_ROWS = 128  # ... of the bfloat16 prompt kernel with tiled TMA loads
 PREFILL_TMA_KEYS = 64   # key positions per tile of that kernel
 DECODE_SPLIT = 128   # key positions per split of the bfloat16 single-token kernel
+
+#: activations the products' epilogues and ``bias_act`` know
+ACTIVATIONS = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2}
 
 
 def _declare(lib: ctypes.CDLL, signatures) -> None:
@@ -249,6 +258,59 @@ class Ops:
             n, dim, table.shape[0], _ptr(self.status), _stream()))
         return out
 
+    def embedding_bigram(self, table, bigram, tokens, pos, req, last_token, out, buckets: int, mul_prev: int,
+                         mul_cur: int) -> torch.Tensor:
+        """``out[t] = table[token] + bigram[hash(previous token, token)]`` (the table's last row for
+        a sequence's first token); ``last_token`` [slots] int32 is the sequences' state: read for a
+        token that opens its sequence's part of the step, then set to the last token brought."""
+        assert table.is_contiguous() and bigram.is_contiguous() and out.is_contiguous()
+        assert table.dtype == bigram.dtype and out.dtype == torch.float32
+        assert tokens.dtype == torch.int32 and last_token.dtype == torch.int32
+        assert bigram.shape == (buckets + 1, table.shape[1])
+        n, dim = out.shape
+        _check(self.lib, self.lib.fg_embedding_bigram(
+            _ptr(table), _ptr(bigram), _code(table.dtype), _ptr(tokens), _ptr(pos), _ptr(req), _ptr(last_token),
+            _ptr(out), n, dim, table.shape[0], int(buckets), int(mul_prev), int(mul_cur), _ptr(self.status),
+            _stream()))
+        Ops.launches += 1  # the state's own launch
+        return out
+
+    def dyt(self, h, pre=None, out=None, delta=None, post=None, rows=None):
+        """Dynamic Tanh around the residual stream ``h`` (float32): ``h += post(delta)`` (``post``
+        and ``delta`` optional), then ``out = pre(h)``.  ``pre`` / ``post`` are ``(alpha, weight,
+        bias)`` float32 device tensors.  With ``rows`` only those rows are computed and ``h`` stays."""
+        assert h.is_contiguous() and h.dtype == torch.float32
+        dim = h.shape[1]
+        n = h.shape[0] if rows is None else rows.numel()
+        if delta is not None:
+            assert delta.is_contiguous() and delta.shape == h.shape
+        if out is not None:
+            assert out.is_contiguous() and out.shape == (n, dim) and pre is not None
+        for params in (pre, post):
+            if params is not None:
+                assert all(t.dtype == torch.float32 and t.is_contiguous() for t in params)
+        pa, pw, pb = post if post is not None else (None, None, None)
+        ra, rw, rb = pre if pre is not None else (None, None, None)
+        _check(self.lib, self.lib.fg_dyt(
+            _ptr(h), _ptr(delta), _code(delta.dtype) if delta is not None else 0, _ptr(pa), _ptr(pw), _ptr(pb),
+            _ptr(ra), _ptr(rw), _ptr(rb), _ptr(out), _code(out.dtype) if out is not None else 0, _ptr(rows),
+            n, dim, _stream()))
+        return out
+
+    def bias_act(self, x: torch.Tensor, act: Optional[str], bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x = act(x + bias)`` in place (float32 arithmetic, one rounding)."""
+        assert x.is_contiguous() and (bias is None or (bias.dtype == x.dtype and bias.is_contiguous()))
+        _check(self.lib, self.lib.fg_bias_act(_ptr(x), _ptr(bias), _code(x.dtype), x.shape[0], x.shape[1],
+                                              ACTIVATIONS[act], _stream()))
+        return x
+
+    def scale_softcap(self, logits: torch.Tensor, scale: float, cap: Optional[float]) -> torch.Tensor:
+        """``logits = cap * tanh(logits * scale / cap)`` in place (only the scaling without a cap)."""
+        assert logits.is_contiguous() and logits.dtype == torch.float32
+        _check(self.lib, self.lib.fg_scale_softcap(_ptr(logits), logits.shape[0], logits.shape[1], float(scale),
+                                                   float(cap or 0.0), _stream()))
+        return logits
+
     def rmsnorm(self, h, weight, eps: float, out=None, delta=None, rows=None):
         """``h += delta`` (if given), then ``out = rmsnorm(h) * weight``.
         With ``out=None`` and a delta only the sum is done.  With ``rows``
@@ -270,11 +332,16 @@ class Ops:
         return out
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """``x @ w.T`` for ``x`` [M, K] and ``w`` [N, K] (fastgen/forward.py:438-440)."""
+               out_dtype: Optional[torch.dtype] = None, bias: Optional[torch.Tensor] = None,
+               act: Optional[str] = None) -> torch.Tensor:
+        """``act(x @ w.T + bias)`` for ``x`` [M, K] and ``w`` [N, K] (fastgen/forward.py:438-440);
+        ``bias`` [N] of the compute dtype and ``act`` (a key of ``ACTIVATIONS``) are optional.  The
+        bias is added to the float32 sums; the activation sees the rounded result."""
         m, k = x.shape
         n = w.shape[0]
         assert w.shape[1] == k and x.stride(1) == 1 and w.stride(1) == 1
+        assert bias is None or (bias.shape == (n,) and bias.dtype == w.dtype and bias.is_contiguous())
+        code = ACTIVATIONS[act]
         if self.act_dtype == torch.float32:
             assert x.dtype == torch.float32 and w.dtype == torch.float32
             if out is None:
@@ -282,7 +349,10 @@ class Ops:
             assert out.dtype == torch.float32 and out.stride(1) == 1
             _check(self.lib, self.lib.fg_gemm_f32_nt(
                 _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
-                m, n, k, _stream()))
+                m, n, k, _ptr(bias), _stream()))
+            if code:
+                assert out.is_contiguous()
+                self.bias_act(out, act)
             return out
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
         want = out.dtype if out is not None else (out_dtype or torch.bfloat16)
@@ -294,10 +364,18 @@ class Ops:
             assert out.stride(1) == 1
             _check(self.lib, self.lib.fg_gemm_skinny_bf16(
                 _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out.dtype),
-                m, n, k, _stream()))
+                m, n, k, _ptr(bias), code, _stream()))
             return out
         if want == torch.bfloat16:
-            return torch.mm(x, w.t(), out=out) if out is not None else torch.mm(x, w.t())
+            # the library adds the bias to its float32 sums: one rounding, as in the kernel above
+            if bias is not None:
+                res = torch.addmm(bias, x, w.t(), out=out) if out is not None else torch.addmm(bias, x, w.t())
+            else:
+                res = torch.mm(x, w.t(), out=out) if out is not None else torch.mm(x, w.t())
+            if code:
+                self.bias_act(res, act)
+            return res
+        assert bias is None and not code, "a float32 result of a bfloat16 product takes no bias or activation"
         # float32 result of a bfloat16 product (logits)
         res = torch.mm(x, w.t(), out_dtype=torch.float32)
         if out is not None:
@@ -325,18 +403,19 @@ class Ops:
         return out
 
     def qkv_rope_write(self, x, wqkv, pos, req, freqs, memory, n_heads: int, n_kv_heads: int,
-                       head_dim: int) -> Optional[torch.Tensor]:
+                       head_dim: int, bias=None, v_freqs=None) -> Optional[torch.Tensor]:
         """Queries, keys and values of a few tokens in one kernel: the product
         against ``[wq; wk; wv]``, the rotation, and the write of keys and
-        values into their pages.  Returns the rotated queries [T, heads*head_dim],
-        or ``None`` when the shapes do not allow it."""
+        values into their pages.  ``bias`` (over the fused rows) is added before the
+        rounding; ``v_freqs`` turns the values by their own position too.  Returns the
+        rotated queries [T, heads*head_dim], or ``None`` when the shapes do not allow it."""
         m, k = x.shape
         if not self._skinny_ok(x, wqkv, k) or head_dim % 16:
             return None
         q = torch.empty((m, n_heads * head_dim), dtype=torch.bfloat16, device=x.device)
         _check(self.lib, self.lib.fg_gemm_skinny_qkv_bf16(
-            _ptr(x), x.stride(0), _ptr(wqkv), wqkv.stride(0), _ptr(q), q.stride(0), m, k,
-            _ptr(pos), _ptr(req), _ptr(freqs), _ptr(memory.k_pages), _ptr(memory.v_pages),
+            _ptr(x), x.stride(0), _ptr(wqkv), wqkv.stride(0), _ptr(q), q.stride(0), m, k, _ptr(bias),
+            _ptr(pos), _ptr(req), _ptr(freqs), _ptr(v_freqs), _ptr(memory.k_pages), _ptr(memory.v_pages),
             _ptr(memory.block_table), memory.block_table.shape[1], memory.page_size,
             memory.k_pages.shape[0], n_heads, n_kv_heads, head_dim, _ptr(self.status), _stream()))
         return q
@@ -351,8 +430,9 @@ class Ops:
         return out
 
     def rope_kv_write(self, q, k, v, pos, req, freqs, k_pages, v_pages, block_table,
-                      page_size: int, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
-        """Rotate ``q`` in place; rotate ``k`` and copy ``v`` into their pages.
+                      page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, v_freqs=None) -> None:
+        """Rotate ``q`` in place; rotate ``k`` and copy ``v`` into their pages (``v`` is
+        rotated too, by the table ``v_freqs``, when that is given).
         ``q``/``k``/``v`` are row-strided views [T, heads*head_dim]; ``k``/``v``
         may both be ``None`` (queries only)."""
         t = q.shape[0]
@@ -368,7 +448,7 @@ class Ops:
         _check(self.lib, self.lib.fg_rope_kv_write(
             _ptr(q), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0,
             _ptr(v), v.stride(0) if v is not None else 0, _code(q.dtype), _ptr(pos), _ptr(req),
-            _ptr(freqs), _ptr(k_pages) if k is not None else None,
+            _ptr(freqs), _ptr(v_freqs) if k is not None else None, _ptr(k_pages) if k is not None else None,
             _ptr(v_pages) if k is not None else None,
             _ptr(block_table) if k is not None else None, width, page_size, n_pages,
             t, n_heads, n_kv_heads, head_dim, _ptr(self.status), _stream()))
@@ -489,6 +569,30 @@ class Ops:
                 _check(lib, lib.fg_attention_decode_bf16(
                     _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *head, _ptr(self.status), _stream()))
             Ops.launches += 1  # the combine kernel
+
+    def rotate_heads(self, x, pos, req, freqs, n_heads: int, head_dim: int) -> torch.Tensor:
+        """Rotate the adjacent pairs of every head of ``x`` [T, heads*head_dim] in place by
+        ``pos * freqs`` (a table of negated frequencies turns them back)."""
+        self.rope_kv_write(x, None, None, pos, req, freqs, None, None, None, 0, n_heads, 0, head_dim)
+        return x
+
+    def attention_sigmoid(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
+                          window: Optional[int], scale: float, gate=None, r1=None, r2=None) -> None:
+        """Paged attention with sigmoid weights, not normalised over the keys:
+        ``sum_j sigmoid(q.k_j * scale + gate[h] - r1[h] * ln(1 + r2[h] * distance)) v_j`` over the
+        visible keys; ``gate``, ``r1``, ``r2`` are float32 [heads] or ``None``.  One CUDA-core kernel
+        with float32 arithmetic serves both storage types, prompt portions and single tokens."""
+        lib = attn(head_dim)
+        k_pages, v_pages, block_table = memory.k_pages, memory.v_pages, memory.block_table
+        assert q.stride(1) == 1 and out.stride(1) == 1
+        for t in (gate, r1, r2):
+            assert t is None or (t.dtype == torch.float32 and t.numel() == n_heads and t.is_contiguous())
+        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, SIMT_ROWS), 1)
+        _check(lib, lib.fg_attention_sigmoid(
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), _ptr(k_pages), _ptr(v_pages),
+            _ptr(block_table), block_table.shape[1], memory.page_size, k_pages.shape[0], _ptr(ctx.pos),
+            _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim,
+            int(window or 0), float(scale), _ptr(gate), _ptr(r1), _ptr(r2), _ptr(self.status), _stream()))
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,
                out_tokens, out_logprobs=None, scratch=None, with_status: bool = False) -> torch.Tensor:

@@ -50,8 +50,8 @@ template <typename T>
 __global__ void __launch_bounds__(ROPE_THREADS)
 rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
                const T* __restrict__ v, int v_stride, const int* __restrict__ pos,
-               const int* __restrict__ req, const float* __restrict__ freqs, T* __restrict__ k_pages,
-               T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
+               const int* __restrict__ req, const float* __restrict__ freqs,
+               const float* __restrict__ v_freqs, T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                int page_size, int n_pages, int n_heads, int n_kv_heads, int head_dim, int* status,
                bool vec, int heads_per_block) {
   const int t = blockIdx.x;
@@ -65,8 +65,9 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
   const int n_kv = (k != nullptr) ? n_kv_heads : 0;
   const int total = n_heads + 2 * n_kv;  // heads in the order q..., k..., v...
   const int h_end = min(total, (int)(blockIdx.y + 1) * heads_per_block);
-  float s = 0.f, c = 1.f;
+  float s = 0.f, c = 1.f, sv = 0.f, cv = 1.f;
   if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
+  if (v_freqs != nullptr) sincosf((float)p * v_freqs[j], &sv, &cv);
   size_t slot = 0;
   bool have_slot = false;
   for (int h = blockIdx.y * heads_per_block + lane_head; h < h_end; h += lanes) {
@@ -91,7 +92,9 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
     const size_t dst = (slot + (size_t)g * page_size) * head_dim + 2 * j;
     if (is_v) {
       const T* x = v + (size_t)t * v_stride + g * head_dim + 2 * j;
-      store_pair<T>(v_pages + dst, load_pair<T>(x, vec), vec);
+      const float2 val = load_pair<T>(x, vec);
+      // values turn by their own table when they have one (cv = 1, sv = 0: a copy)
+      store_pair<T>(v_pages + dst, make_float2(val.x * cv - val.y * sv, val.y * cv + val.x * sv), vec);
     } else {
       const T* x = k + (size_t)t * k_stride + g * head_dim + 2 * j;
       const float2 val = load_pair<T>(x, vec);
@@ -109,7 +112,7 @@ __global__ void __launch_bounds__(ROPE_THREADS)
 rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k, int k_stride,
                       const __nv_bfloat16* __restrict__ v, int v_stride, const int* __restrict__ pos,
                       const int* __restrict__ req, const float* __restrict__ freqs,
-                      __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                      const float* __restrict__ v_freqs, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                       const int* __restrict__ block_table, int table_width, int page_size, int n_pages,
                       int n_heads, int n_kv_heads, int head_dim, int* status, int heads_per_block) {
   const int t = blockIdx.x;
@@ -123,12 +126,13 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
   const int n_kv = (k != nullptr) ? n_kv_heads : 0;
   const int total = n_heads + 2 * n_kv;  // heads in the order q..., k..., v...
   const int h_end = min(total, (int)(blockIdx.y + 1) * heads_per_block);
-  float sn[4], cs[4];
+  float sn[4], cs[4], snv[4], csv[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    sn[i] = 0.f;
-    cs[i] = 1.f;
+    sn[i] = snv[i] = 0.f;
+    cs[i] = csv[i] = 1.f;
     if (freqs != nullptr) sincosf((float)p * freqs[piece * 4 + i], &sn[i], &cs[i]);
+    if (v_freqs != nullptr) sincosf((float)p * v_freqs[piece * 4 + i], &snv[i], &csv[i]);
   }
   size_t slot = 0;
   if (n_kv > 0) {
@@ -146,6 +150,15 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
     for (int i = 0; i < 4; ++i) {
       const float2 val = __bfloat1622float2(h2[i]);
       h2[i] = __floats2bfloat162_rn(val.x * cs[i] - val.y * sn[i], val.y * cs[i] + val.x * sn[i]);
+    }
+    return raw;
+  };
+  auto rotate_v = [&](uint4 raw) {
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 val = __bfloat1622float2(h2[i]);
+      h2[i] = __floats2bfloat162_rn(val.x * csv[i] - val.y * snv[i], val.y * csv[i] + val.x * snv[i]);
     }
     return raw;
   };
@@ -173,17 +186,19 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
       const bool is_v = h >= n_heads + n_kv;
       const int g = h - n_heads - (is_v ? n_kv : 0);
       const size_t dst = (slot + (size_t)g * page_size) * head_dim + piece * 8;
-      *reinterpret_cast<uint4*>((is_v ? v_pages : k_pages) + dst) = is_v ? raw[u] : rotate(raw[u]);
+      *reinterpret_cast<uint4*>((is_v ? v_pages : k_pages) + dst) =
+          is_v ? (v_freqs != nullptr ? rotate_v(raw[u]) : raw[u]) : rotate(raw[u]);
     }
   }
 }
 
 // q: [T, n_heads*head_dim] with row stride q_stride (elements), rotated in place.
 // k, v: [T, n_kv_heads*head_dim] with their strides, or both null (queries only).
-// freqs: float32 [head_dim/2] or null for no rotation.
+// freqs: float32 [head_dim/2] or null for no rotation of queries and keys; v_freqs: the same
+// for values, which are rotated by their own position on their way into the page (null: copied).
 extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stride, const void* v,
                                 int v_stride, int dtype, const int* pos, const int* req,
-                                const float* freqs, void* k_pages, void* v_pages,
+                                const float* freqs, const float* v_freqs, void* k_pages, void* v_pages,
                                 const int* block_table, int table_width, int page_size, int n_pages,
                                 int n_tokens, int n_heads, int n_kv_heads, int head_dim, int* status,
                                 cudaStream_t stream) {
@@ -209,20 +224,20 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
       ok16(v, v_stride) && ok16(k_pages, 0) && ok16(v_pages, 0)) {
     rope_kv_bf16x8_kernel<<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, pos, req,
-        freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages,
-        n_heads, n_kv_heads, head_dim, status, ipt);
+        freqs, v_freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width, page_size,
+        n_pages, n_heads, n_kv_heads, head_dim, status, ipt);
     FG_CHECK_LAUNCH("fg_rope_kv_write");
     return 0;
   }
   if (dtype == FG_F32)
     rope_kv_kernel<float><<<grid, threads, 0, stream>>>(
-        (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, pos, req, freqs,
+        (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, pos, req, freqs, v_freqs,
         (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_pages, n_heads,
         n_kv_heads, head_dim, status, vec, ipt);
   else if (dtype == FG_BF16)
     rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
-        v_stride, pos, req, freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
+        v_stride, pos, req, freqs, v_freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
         table_width, page_size, n_pages, n_heads, n_kv_heads, head_dim, status, vec, ipt);
   else
     FG_CHECK_ARG(false, "fg_rope_kv_write: bad dtype %d", dtype);

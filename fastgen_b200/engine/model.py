@@ -13,17 +13,21 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from ..config import ModelArgs, load_model_args
+from ..config import ModelArgs, PartSpec, load_model_args
 from ..parts.base import (
     Block,
     CacheSpec,
+    Embedder,
     StateSpec,
     WeightSpec,
     make_block,
+    make_embedder,
     make_feed_forward,
     make_mixer,
     make_norm,
+    split_pending,
 )
+from ..parts.params import TableEmbeddingParams
 from ..weights.loader import load_weights
 
 
@@ -43,29 +47,30 @@ def _build_blocks(args: ModelArgs) -> List[Block]:
                 layer.block,
                 make_mixer(layer.mixer),
                 make_norm(layer.mixer_norm),
-                make_feed_forward(layer.ffn),
-                make_norm(layer.ffn_norm),
+                make_feed_forward(layer.ffn) if layer.ffn is not None else None,
+                make_norm(layer.ffn_norm) if layer.ffn_norm is not None else None,
                 **extra,
             )
         )
     return blocks
 
 
-def _embedding_specs(args: ModelArgs) -> List[WeightSpec]:
-    specs = [WeightSpec(args.embedding_name, (args.vocab_size, args.dim))]
-    if not args.tie_embeddings:
-        specs.append(WeightSpec(args.output_name, (args.vocab_size, args.dim)))
-    return specs
+def _build_embedder(args: ModelArgs) -> Embedder:
+    spec = args.embedder
+    if spec is None:
+        spec = PartSpec("table", TableEmbeddingParams(args.vocab_size, args.dim), {"table": args.embedding_name})
+    return make_embedder(spec)
 
 
-def _collect_specs(args: ModelArgs, blocks: Sequence[Block], final_norm) -> List[WeightSpec]:
+def _collect_specs(args: ModelArgs, blocks: Sequence[Block], final_norm, embedder: Embedder) -> List[WeightSpec]:
     specs: Dict[str, WeightSpec] = {}
-    ordered = [_embedding_specs(args)[0]]
+    ordered = list(embedder.weight_specs())
     for block in blocks:
         for part in block.parts():
             ordered.extend(part.weight_specs())
     ordered.extend(final_norm.weight_specs())
-    ordered.extend(_embedding_specs(args)[1:])
+    if not args.tie_embeddings:
+        ordered.append(WeightSpec(args.output_name, (args.vocab_size, args.dim)))
     for s in ordered:
         if s.name in specs and specs[s.name].shape != s.shape:
             raise ValueError(f"tensor {s.name} is asked for with two shapes")
@@ -75,7 +80,7 @@ def _collect_specs(args: ModelArgs, blocks: Sequence[Block], final_norm) -> List
 
 def model_weight_specs(args: ModelArgs) -> List[WeightSpec]:
     """Every checkpoint tensor a model of this description needs, in a fixed order."""
-    return _collect_specs(args, _build_blocks(args), make_norm(args.final_norm))
+    return _collect_specs(args, _build_blocks(args), make_norm(args.final_norm), _build_embedder(args))
 
 
 class Model:
@@ -86,18 +91,22 @@ class Model:
         self.ops = ops
         self.blocks = _build_blocks(args)
         self.final_norm = make_norm(args.final_norm)
+        self.embedder = _build_embedder(args)
         self.embedding: Optional[torch.Tensor] = None
         self.output: Optional[torch.Tensor] = None
 
     # -- description -----------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:
-        return _collect_specs(self.args, self.blocks, self.final_norm)
+        return _collect_specs(self.args, self.blocks, self.final_norm, self.embedder)
 
     def cache_specs(self) -> List[Optional[CacheSpec]]:
         return [self.blocks[e.layer].mixer.cache_spec() for e in self.args.schedule]
 
     def state_specs(self) -> List[Optional[StateSpec]]:
         return [self.blocks[e.layer].mixer.state_spec() for e in self.args.schedule]
+
+    def embedder_state_spec(self) -> Optional[StateSpec]:
+        return self.embedder.state_spec()
 
     def kv_from(self) -> List[Optional[int]]:
         return [e.kv_from for e in self.args.schedule]
@@ -132,7 +141,8 @@ class Model:
     # -- weights -----------------------------------------------------------------
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         dt = self.ops.act_dtype
-        self.embedding = tensors[self.args.embedding_name].to(dt).contiguous()
+        self.embedder.bind({local: tensors[name] for local, name in self.embedder.names.items()}, self.ops)
+        self.embedding = self.embedder.table()
         if self.args.tie_embeddings:
             self.output = self.embedding
         else:
@@ -152,6 +162,7 @@ class Model:
         args = load_model_args(model_dir)
         model = Model(args, Ops(dtype, device))
         ignore = [args.output_name or "lm_head.weight"] if args.tie_embeddings else []
+        ignore += list(args.optional_tensors)
         tensors = load_weights(model_dir, model.weight_specs(), device, ignore=ignore)
         model.bind(tensors)
         del tensors
@@ -170,7 +181,7 @@ class Model:
             if spec.init[0] == "normal":
                 t = torch.empty(spec.shape, dtype=torch.bfloat16, device=device)
                 t.normal_(0.0, spec.init[1], generator=gen)
-            elif spec.init[0] == "ones":
+            elif spec.init[0] in ("ones", "ones_jitter"):
                 t = torch.ones(spec.shape, dtype=torch.bfloat16, device=device)
             else:
                 t = torch.randint(0, spec.init[1], spec.shape, generator=gen, device=device, dtype=torch.int32)
@@ -181,18 +192,24 @@ class Model:
     # -- forward -----------------------------------------------------------------
     def forward(self, ctx, memories) -> Optional[torch.Tensor]:
         """Run the step's tokens through the schedule.  Returns float32 logits
-        ``[len(ctx.want_rows), vocab]`` (``None`` when no logits are wanted)."""
+        ``[len(ctx.want_rows), vocab]`` (``None`` when no logits are wanted).
+        ``memories`` is the cache's :class:`~fastgen_b200.cache.StepMemories`: one
+        ``LayerMemory`` per schedule entry, and the state of an embedder that keeps one."""
         ops = self.ops
         t = ctx.n_tokens
         h = torch.empty((t, self.args.dim), dtype=torch.float32, device=ops.device)
-        ops.embedding(self.embedding, ctx.tokens, h)
+        self.embedder.forward(ctx, getattr(memories, "embedder_state", None), h)
         pending = None
         for e, entry in enumerate(self.args.schedule):
             h, pending = self.blocks[entry.layer].forward(h, pending, ctx, memories[e])
         if ctx.n_want == 0:
             return None
-        if pending is None:
+        delta, delta_norm = split_pending(pending)
+        if delta is None:
             x = self.final_norm.forward(h, rows=ctx.want_rows)
         else:
-            x = self.final_norm.add_forward(h, pending, rows=ctx.want_rows)
-        return ops.linear(x, self.output, out_dtype=torch.float32)
+            x = self.final_norm.add_forward(h, delta, rows=ctx.want_rows, delta_norm=delta_norm)
+        logits = ops.linear(x, self.output, out_dtype=torch.float32)
+        if self.args.logit_scale != 1.0 or self.args.logit_softcap:
+            ops.scale_softcap(logits, self.args.logit_scale, self.args.logit_softcap)
+        return logits

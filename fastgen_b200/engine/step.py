@@ -205,8 +205,9 @@ class Engine:
             dtype=model.ops.act_dtype,
             device=self.device,
             tensor_map_factory=model.ops.make_kv_tensor_maps,
+            embedder_state=model.embedder_state_spec(),
         )
-        self.memories = [self.cache.memory(e) for e in range(len(args.schedule))]
+        self.memories = self.cache.memories()
         self.last_h2d_bytes = 0
         if use_graphs is None:
             use_graphs = not bool(os.environ.get("FG_NO_CUDA_GRAPHS"))

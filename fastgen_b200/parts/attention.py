@@ -7,7 +7,7 @@ from typing import List, Optional
 import torch
 
 from .base import CacheSpec, Mixer, WeightSpec, make_position, register_mixer
-from .params import AttentionParams
+from .params import AttentionParams, SigmoidAttentionParams
 
 
 def interleave_rope_rows(w: torch.Tensor, n_heads: int) -> torch.Tensor:
@@ -22,6 +22,29 @@ def interleave_rope_rows(w: torch.Tensor, n_heads: int) -> torch.Tensor:
     return w[idx.permute(0, 2, 1).reshape(-1)]
 
 
+def pair_rows_adjacent(w: torch.Tensor, n_heads: int, rot_dims: int) -> torch.Tensor:
+    """Reorder the rows of each head of ``w`` [heads * size, ...] so that the rotated pairs of the
+    half-split layout, ``(i, i + rot_dims/2)`` among a head's first ``rot_dims`` rows, become the
+    adjacent pairs ``(2i, 2i + 1)``; a head's other rows stay where they are."""
+    size = w.shape[0] // n_heads
+    half = rot_dims // 2
+    within = torch.arange(size)
+    within[: rot_dims : 2] = torch.arange(half)
+    within[1 : rot_dims : 2] = torch.arange(half) + half
+    idx = (torch.arange(n_heads)[:, None] * size + within[None, :]).reshape(-1)
+    return w[idx.to(w.device)]
+
+
+def pad_heads(w: torch.Tensor, n_heads: int, size: int) -> torch.Tensor:
+    """Zero rows after each head of ``w`` [heads * s, ...] so that a head has ``size`` rows."""
+    s = w.shape[0] // n_heads
+    if s == size:
+        return w
+    out = w.new_zeros((n_heads, size, *w.shape[1:]))
+    out[:, :s] = w.reshape(n_heads, s, *w.shape[1:])
+    return out.reshape(n_heads * size, *w.shape[1:])
+
+
 class GQAAttention(Mixer):
     """``wo(attention(rope(wq x), rope(wk x), wv x))`` (fastgen/forward.py:438-472).
 
@@ -29,6 +52,13 @@ class GQAAttention(Mixer):
     bind time.  Keys and values of the step's tokens are written to this run's
     cache pages before attention reads them back, so a prompt portion attends to
     itself through the cache exactly as a decoded token does.
+
+    Options of the parameters: biases on the four projections; a value head size of its own
+    (heads are padded with zero rows to one kernel head size, see
+    ``AttentionParams.kernel_head_dim``); rotary encodings that turn a part of the head, in
+    either pairing (half-split rows are reordered at bind time, which changes no score);
+    values turned by their position on their way into the cache and outputs turned back by
+    the query's position.
     """
 
     params: AttentionParams
@@ -38,34 +68,86 @@ class GQAAttention(Mixer):
         super().__init__(spec)
         p = self.params
         self.position = make_position(p.position)
+        self.value_position = make_position(p.value_position) if p.value_position is not None else None
         self.scale = p.softmax_scale if p.softmax_scale is not None else p.head_dim ** -0.5
-        self.q_width = p.n_heads * p.head_dim
-        self.kv_width = p.n_kv_heads * p.head_dim
+        self.v_head_dim = p.v_head_dim or p.head_dim
+        self.hd = p.kernel_head_dim
+        self.q_width = p.n_heads * self.hd
+        self.kv_width = p.n_kv_heads * self.hd
 
     def weight_specs(self) -> List[WeightSpec]:
         p = self.params
-        return [
-            WeightSpec(self.names["wq"], (self.q_width, p.dim)),
-            WeightSpec(self.names["wk"], (self.kv_width, p.dim)),
-            WeightSpec(self.names["wv"], (self.kv_width, p.dim)),
-            WeightSpec(self.names["wo"], (p.dim, self.q_width)),
+        q, k, v = p.n_heads * p.head_dim, p.n_kv_heads * p.head_dim, p.n_kv_heads * self.v_head_dim
+        o = p.n_heads * self.v_head_dim
+        specs = [
+            WeightSpec(self.names["wq"], (q, p.dim)),
+            WeightSpec(self.names["wk"], (k, p.dim)),
+            WeightSpec(self.names["wv"], (v, p.dim)),
+            WeightSpec(self.names["wo"], (p.dim, o)),
         ]
+        if p.bias:
+            specs += [
+                WeightSpec(self.names["bq"], (q,)),
+                WeightSpec(self.names["bk"], (k,)),
+                WeightSpec(self.names["bv"], (v,)),
+                WeightSpec(self.names["bo"], (p.dim,)),
+            ]
+        return specs
 
     def cache_spec(self) -> Optional[CacheSpec]:
         p = self.params
-        return CacheSpec(p.n_kv_heads, p.head_dim, p.window)
+        return CacheSpec(p.n_kv_heads, self.hd, p.window)
+
+    def _rot_dims(self, position, size: int) -> int:
+        params = getattr(position, "params", None)
+        return getattr(params, "rot_dims", None) or size
+
+    def _rows(self, t: torch.Tensor, n_heads: int, size: int, layout: str, position) -> torch.Tensor:
+        """A projection's rows (or its bias) as the kernels want them: rotated pairs adjacent,
+        heads padded to the kernel head size."""
+        if layout == "half_split" and position is not None:
+            t = pair_rows_adjacent(t, n_heads, self._rot_dims(position, size))
+        return pad_heads(t, n_heads, self.hd)
 
     def bind(self, tensors, ops) -> None:
         p = self.params
         self.ops = ops
         dt = ops.act_dtype
-        wq, wk = tensors["wq"], tensors["wk"]
-        if p.qk_layout == "half_split":
-            wq = interleave_rope_rows(wq, p.n_heads)
-            wk = interleave_rope_rows(wk, p.n_kv_heads)
-        self.wqkv = torch.cat([wq, wk, tensors["wv"]], dim=0).to(dt).contiguous()
-        self.wo = tensors["wo"].to(dt).contiguous()
-        self.freqs = self.position.table(ops.device)
+        vd = self.v_head_dim
+        rotates = not isinstance(self.position.table(ops.device), type(None))
+        qk_pos = self.position if rotates else None
+        wq = self._rows(tensors["wq"], p.n_heads, p.head_dim, p.qk_layout, qk_pos)
+        wk = self._rows(tensors["wk"], p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos)
+        wv = self._rows(tensors["wv"], p.n_kv_heads, vd, p.v_layout, self.value_position)
+        self.wqkv = torch.cat([wq, wk, wv], dim=0).to(dt).contiguous()
+        # the output projection's columns follow the value heads' rows
+        wo_t = self._rows(tensors["wo"].t(), p.n_heads, vd, p.v_layout, self.value_position)
+        self.wo = wo_t.t().to(dt).contiguous()
+        self.bqkv = self.bo = None
+        if p.bias:
+            bq = self._rows(tensors["bq"], p.n_heads, p.head_dim, p.qk_layout, qk_pos)
+            bk = self._rows(tensors["bk"], p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos)
+            bv = self._rows(tensors["bv"], p.n_kv_heads, vd, p.v_layout, self.value_position)
+            self.bqkv = torch.cat([bq, bk, bv], dim=0).to(dt).contiguous()
+            self.bo = tensors["bo"].to(dt).contiguous()
+        self.freqs = self._table(self.position)
+        self.v_freqs = self.v_unfreqs = None
+        if self.value_position is not None:
+            self.v_freqs = self._table(self.value_position)
+            if self.v_freqs is not None:
+                self.v_unfreqs = (-self.v_freqs).contiguous()
+
+    def _table(self, position) -> Optional[torch.Tensor]:
+        """A position encoding's frequency table over the kernel head size: the pairs of a
+        head's padding have frequency zero."""
+        table = position.table(self.ops.device)
+        if table is not None and table.numel() < self.hd // 2:
+            table = torch.cat([table, table.new_zeros(self.hd // 2 - table.numel())]).contiguous()
+        return table
+
+    def _attend(self, q, o, ctx, memory) -> None:
+        p = self.params
+        self.ops.attention(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale)
 
     def forward(self, x, ctx, memory):
         p, ops = self.params, self.ops
@@ -74,26 +156,62 @@ class GQAAttention(Mixer):
         if memory.writes and x.dtype == torch.bfloat16:
             # a few tokens: projection, rotation and page write in one kernel
             q = ops.qkv_rope_write(x, self.wqkv, ctx.pos, ctx.req, self.freqs, memory,
-                                   p.n_heads, p.n_kv_heads, p.head_dim)
+                                   p.n_heads, p.n_kv_heads, self.hd, bias=self.bqkv, v_freqs=self.v_freqs)
         if q is None:
             if memory.writes:
-                qkv = ops.linear(x, self.wqkv)
+                qkv = ops.linear(x, self.wqkv, bias=self.bqkv)
                 q = qkv[:, : self.q_width]
                 k = qkv[:, self.q_width : self.q_width + self.kv_width]
                 v = qkv[:, self.q_width + self.kv_width :]
             else:
                 # this run reads another run's cache: only queries are needed
-                q = ops.linear(x, self.wqkv[: self.q_width])
+                bq = self.bqkv[: self.q_width] if self.bqkv is not None else None
+                q = ops.linear(x, self.wqkv[: self.q_width], bias=bq)
                 k = v = None
             ops.rope_kv_write(
                 q, k, v, ctx.pos, ctx.req, self.freqs, memory.k_pages, memory.v_pages,
-                memory.block_table, memory.page_size, p.n_heads, p.n_kv_heads, p.head_dim,
+                memory.block_table, memory.page_size, p.n_heads, p.n_kv_heads, self.hd, v_freqs=self.v_freqs,
             )
         o = torch.empty((t, self.q_width), dtype=x.dtype, device=x.device)
-        ops.attention(
-            q, o, memory, ctx, p.n_heads, p.n_kv_heads, p.head_dim, p.window, self.scale,
-        )
-        return ops.linear(o, self.wo)
+        self._attend(q, o, ctx, memory)
+        if self.v_unfreqs is not None:
+            # the sum over values that were turned by their own positions is turned back by the query's
+            ops.rotate_heads(o, ctx.pos, ctx.req, self.v_unfreqs, p.n_heads, self.hd)
+        return ops.linear(o, self.wo, bias=self.bo)
+
+
+class SigmoidAttention(GQAAttention):
+    """Attention with sigmoid weights that are not normalised over the keys:
+    ``sum_j sigmoid(q.k_j * scale + gate_h - r1_h ln(1 + r2_h (i - j))) v_j`` over the visible
+    keys (causal, with the window of the parameters).  Projections, cache and options are
+    those of :class:`GQAAttention`; the per-head numbers are the tensors ``gate``, ``r1``, ``r2``."""
+
+    params: SigmoidAttentionParams
+
+    def weight_specs(self) -> List[WeightSpec]:
+        p = self.params
+        specs = super().weight_specs()
+        if p.distance_bias:
+            specs += [
+                WeightSpec(self.names["r1"], (p.n_heads,), ("ones",)),
+                WeightSpec(self.names["r2"], (p.n_heads,), ("ones",)),
+            ]
+        if p.gate:
+            specs.append(WeightSpec(self.names["gate"], (p.n_heads,), ("normal", 0.5)))
+        return specs
+
+    def bind(self, tensors, ops) -> None:
+        super().bind(tensors, ops)
+        p = self.params
+        self.r1 = tensors["r1"].float().contiguous() if p.distance_bias else None
+        self.r2 = tensors["r2"].float().contiguous() if p.distance_bias else None
+        self.gate = tensors["gate"].float().contiguous() if p.gate else None
+
+    def _attend(self, q, o, ctx, memory) -> None:
+        p = self.params
+        self.ops.attention_sigmoid(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale,
+                                   gate=self.gate, r1=self.r1, r2=self.r2)
 
 
 register_mixer("gqa_attention", GQAAttention)
+register_mixer("sigmoid_attention", SigmoidAttention)

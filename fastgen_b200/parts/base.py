@@ -60,9 +60,11 @@ class CacheSpec:
 
 @dataclass(frozen=True)
 class StateSpec:
-    """Fixed-size per-request state of a mixer (float32, zeroed on admission)."""
+    """Fixed-size per-request state of a mixer or of the embedder (zeroed on admission;
+    float32 unless ``dtype`` says otherwise)."""
 
     shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
 
 
 class Part:
@@ -90,15 +92,40 @@ class Norm(Part):
         tensor ``rows`` when it is given)."""
         raise NotImplementedError
 
-    def add_forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows=None) -> torch.Tensor:
+    def add_forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows=None,
+                    delta_norm: Optional["Norm"] = None) -> torch.Tensor:
         """``h += delta`` (32-bit sum; ``delta`` may be ``None``) and return
-        ``norm(h)``.  With ``rows`` only those rows are computed and ``h`` may
+        ``norm(h)``.  With ``delta_norm`` the summand is ``delta_norm(delta)``: the
+        norm that closes a sub-layer whose output is normed before it joins the
+        residual stream.  With ``rows`` only those rows are computed and ``h`` may
         be left as it was.
 
-        The default composes the two; implementations may fuse them."""
+        The default composes the steps; implementations may fuse them."""
         if delta is not None:
+            if delta_norm is not None:
+                delta = delta_norm.forward(delta, out_dtype=torch.float32)
+            if rows is not None:
+                h = h.index_select(0, rows.long()) + delta.index_select(0, rows.long()).to(h.dtype)
+                return self.forward(h)
             h.add_(delta.to(h.dtype))
         return self.forward(h, rows=rows)
+
+
+@dataclass
+class NormedDelta:
+    """A summand that has not joined the residual stream yet, with the norm it passes
+    through on its way (``None``: none).  Blocks hand it on as ``pending`` so that the sum
+    can be fused with the next norm."""
+
+    delta: torch.Tensor
+    norm: Optional[Norm] = None
+
+
+def split_pending(pending):
+    """``(delta, its norm)`` of what a block handed on: a tensor, a :class:`NormedDelta` or ``None``."""
+    if isinstance(pending, NormedDelta):
+        return pending.delta, pending.norm
+    return pending, None
 
 
 class PositionEncoding(Part):
@@ -109,6 +136,22 @@ class PositionEncoding(Part):
     rotation)."""
 
     def table(self, device) -> Optional[torch.Tensor]:
+        raise NotImplementedError
+
+
+class Embedder(Part):
+    """From token ids to the first residual stream.  ``forward`` fills ``out`` [T, dim]
+    (float32) for the step's tokens; an embedder that keeps something per request between
+    steps says so with ``state_spec`` and finds it in ``state`` (indexed by slot)."""
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def table(self) -> torch.Tensor:
+        """The token table [vocab, dim] (what a tied output projection uses)."""
+        raise NotImplementedError
+
+    def forward(self, ctx, state: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -139,7 +182,8 @@ class FeedForward(Part):
 class Block:
     """Arrangement of a layer's parts around the residual stream."""
 
-    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm, **extra: Part):
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: Optional[FeedForward], ffn_norm: Optional[Norm],
+                 **extra: Part):
         self.mixer = mixer
         self.mixer_norm = mixer_norm
         self.ffn = ffn
@@ -148,7 +192,8 @@ class Block:
         self.extra: Dict[str, Part] = dict(extra)
 
     def parts(self) -> Sequence[Part]:
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, *self.extra.values())
+        parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, *self.extra.values())
+        return tuple(p for p in parts if p is not None)
 
     def forward(self, h, pending, ctx, memory):
         """Run the layer.  ``h`` is the residual stream [T, dim] (float32) and
@@ -162,6 +207,15 @@ _FEED_FORWARDS: Dict[str, Callable[[PartSpec], FeedForward]] = {}
 _NORMS: Dict[str, Callable[[PartSpec], Norm]] = {}
 _POSITIONS: Dict[str, Callable[[PartSpec], PositionEncoding]] = {}
 _BLOCKS: Dict[str, Callable[..., Block]] = {}
+_EMBEDDERS: Dict[str, Callable[[PartSpec], Embedder]] = {}
+
+
+def register_embedder(kind: str, factory) -> None:
+    _EMBEDDERS[kind] = factory
+
+
+def make_embedder(spec: PartSpec) -> Embedder:
+    return _make(_EMBEDDERS, "embedder", spec)
 
 
 def register_mixer(kind: str, factory) -> None:

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from .base import Block, register_block
+from .base import Block, NormedDelta, register_block, split_pending
 
 
 class PreNormBlock(Block):
@@ -14,10 +14,33 @@ class PreNormBlock(Block):
     """
 
     def forward(self, h, pending, ctx, memory):
-        a = self.mixer_norm.add_forward(h, pending)
+        delta, delta_norm = split_pending(pending)
+        a = self.mixer_norm.add_forward(h, delta, delta_norm=delta_norm)
         m = self.mixer.forward(a, ctx, memory)
         f = self.ffn_norm.add_forward(h, m)
         return h, self.ffn.forward(f, ctx)
 
 
+class SandwichBlock(Block):
+    """Norms before and after each sub-layer:
+    ``h = h + post_mixer_norm(mixer(norm(h))); h = h + post_ffn_norm(ffn(norm(h)))``.
+
+    The two closing norms are the extra parts ``post_mixer_norm`` and ``post_ffn_norm``.  A
+    sub-layer's output is handed on together with its closing norm, so that a norm which can
+    (Dynamic Tanh) applies the closing norm, adds to the residual stream and norms the sum in
+    one kernel.  A layer without a feed-forward (``ffn`` is ``None``) ends after the mixer.
+    """
+
+    def forward(self, h, pending, ctx, memory):
+        delta, delta_norm = split_pending(pending)
+        a = self.mixer_norm.add_forward(h, delta, delta_norm=delta_norm)
+        m = self.mixer.forward(a, ctx, memory)
+        post_mixer = self.extra.get("post_mixer_norm")
+        if self.ffn is None:
+            return h, NormedDelta(m, post_mixer)
+        f = self.ffn_norm.add_forward(h, m, delta_norm=post_mixer)
+        return h, NormedDelta(self.ffn.forward(f, ctx), self.extra.get("post_ffn_norm"))
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)

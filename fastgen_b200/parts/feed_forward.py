@@ -1,4 +1,4 @@
-"""Dense SwiGLU feed-forward."""
+"""Dense feed-forwards: gated (SwiGLU) and plain (up, activation, down)."""
 
 from __future__ import annotations
 
@@ -7,7 +7,7 @@ from typing import List
 import torch
 
 from .base import FeedForward, WeightSpec, register_feed_forward
-from .params import SwiGLUParams
+from .params import DenseMLPParams, SwiGLUParams
 
 
 class SwiGLU(FeedForward):
@@ -54,4 +54,29 @@ class SwiGLU(FeedForward):
         return ops.linear(g, self.w2)
 
 
+class DenseMLP(FeedForward):
+    """``down(act(up x))``.  The activation is computed in float32 on the rounded product and
+    rounded once; for a few tokens it is the epilogue of the up projection's kernel."""
+
+    params: DenseMLPParams
+
+    def weight_specs(self) -> List[WeightSpec]:
+        p = self.params
+        return [
+            WeightSpec(self.names["up"], (p.ffn_dim, p.dim)),
+            WeightSpec(self.names["down"], (p.dim, p.ffn_dim)),
+        ]
+
+    def bind(self, tensors, ops) -> None:
+        self.ops = ops
+        dt = ops.act_dtype
+        self.up = tensors["up"].to(dt).contiguous()
+        self.down = tensors["down"].to(dt).contiguous()
+
+    def forward(self, x, ctx):
+        ops = self.ops
+        return ops.linear(ops.linear(x, self.up, act=self.params.act), self.down)
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("dense_mlp", DenseMLP)

@@ -7,7 +7,7 @@ from typing import List
 import torch
 
 from .base import Norm, WeightSpec, register_norm
-from .params import RMSNormParams
+from .params import DynamicTanhParams, RMSNormParams
 
 
 class RMSNorm(Norm):
@@ -34,11 +34,59 @@ class RMSNorm(Norm):
         out = torch.empty((n, x.shape[1]), dtype=out_dtype or self.ops.act_dtype, device=x.device)
         return self.ops.rmsnorm(x, self.weight, self.params.eps, out=out, rows=rows)
 
-    def add_forward(self, h, delta, rows=None):
+    def add_forward(self, h, delta, rows=None, delta_norm=None):
         """``h += delta`` in float32 (stored back unless ``rows`` gathers), then the norm."""
+        if delta_norm is not None:
+            return super().add_forward(h, delta, rows=rows, delta_norm=delta_norm)
         n = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, h.shape[1]), dtype=self.ops.act_dtype, device=h.device)
         return self.ops.rmsnorm(h, self.weight, self.params.eps, out=out, delta=delta, rows=rows)
 
 
+class DynamicTanh(Norm):
+    """``tanh(alpha * x) * w + b`` in float32, with a scalar ``alpha`` and vectors ``w``, ``b``
+    (tensors ``weight``, ``bias``, ``alpha``): elementwise, no mean and no variance.
+
+    The sum that precedes the norm is fused into its kernel, and so is the norm of the
+    summand when that is a Dynamic Tanh too: ``h += tanh(a' d) w' + b'; out = tanh(a h) w + b``
+    is one launch.
+    """
+
+    params: DynamicTanhParams
+
+    def weight_specs(self) -> List[WeightSpec]:
+        d = self.params.dim
+        return [
+            WeightSpec(self.names["weight"], (d,), ("ones",)),
+            WeightSpec(self.names["bias"], (d,), ("normal", 0.02)),
+            WeightSpec(self.names["alpha"], (), ("ones",)),
+        ]
+
+    def bind(self, tensors, ops) -> None:
+        self.ops = ops
+        # small vectors: float32 whatever they were stored in (the arithmetic is float32)
+        self.weight = tensors["weight"].float().contiguous()
+        self.bias = tensors["bias"].float().contiguous()
+        self.alpha = tensors["alpha"].float().reshape(1).contiguous()
+
+    def triple(self):
+        return (self.alpha, self.weight, self.bias)
+
+    def forward(self, x, out_dtype=None, rows=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, x.shape[1]), dtype=out_dtype or self.ops.act_dtype, device=x.device)
+        if x.dtype != torch.float32:
+            x = x.float()
+        return self.ops.dyt(x, self.triple(), out, rows=rows)
+
+    def add_forward(self, h, delta, rows=None, delta_norm=None):
+        if delta is not None and delta_norm is not None and not isinstance(delta_norm, DynamicTanh):
+            delta, delta_norm = delta_norm.forward(delta, out_dtype=torch.float32), None
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, h.shape[1]), dtype=self.ops.act_dtype, device=h.device)
+        post = delta_norm.triple() if delta is not None and delta_norm is not None else None
+        return self.ops.dyt(h, self.triple(), out, delta=delta, post=post, rows=rows)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("dynamic_tanh", DynamicTanh)

@@ -23,11 +23,25 @@ class Llama3Scaling:
 
 @dataclass(frozen=True)
 class RopeParams:
-    """Rotary position encoding over adjacent pairs (fastgen/kernels/rope.py:77-89)."""
+    """Rotary position encoding over adjacent pairs (fastgen/kernels/rope.py:77-89).
+
+    ``rot_dims`` (even, at most ``head_dim``): only that many dimensions of a head turn, pair
+    ``i`` by ``pos * theta^(-2i / rot_dims)``; the rest pass unchanged (``None``: all of them).
+    ``linear_factor`` divides every frequency (positions stretched linearly).  The table's
+    entries beyond the rotated pairs are zero, which turns nothing.
+    """
 
     head_dim: int
     theta: float
     scaling: Optional[Llama3Scaling] = None
+    rot_dims: Optional[int] = None
+    linear_factor: Optional[float] = None
+
+    def __post_init__(self) -> None:
+        if self.rot_dims is not None and (self.rot_dims <= 0 or self.rot_dims % 2 or self.rot_dims > self.head_dim):
+            raise ValueError(f"{self.rot_dims} rotated dimensions do not fit a head of {self.head_dim}")
+        if self.linear_factor is not None and self.linear_factor <= 0:
+            raise ValueError(f"a linear scaling factor must be positive, got {self.linear_factor}")
 
 
 @dataclass(frozen=True)
@@ -57,22 +71,51 @@ class AttentionParams:
     window: Optional[int] = None
     softmax_scale: Optional[float] = None  # None: head_dim ** -0.5 (forward.py:221)
     qk_layout: str = "adjacent"
+    #: size of a value head when it differs from the query/key size (``None``: ``head_dim``)
+    v_head_dim: Optional[int] = None
+    #: the four projections carry biases (tensors ``bq``, ``bk``, ``bv``, ``bo``)
+    bias: bool = False
+    #: a ``PartSpec`` of a position encoding for the values: the value of position j is turned by
+    #: j before it is cached and a head's output at position i is turned back by i, so that the
+    #: output sees values turned by j - i.  ``v_layout`` is the checkpoint's pairing of a value
+    #: head's dimensions, as ``qk_layout`` is for queries and keys.
+    value_position: Optional[object] = None
+    v_layout: str = "adjacent"
 
     def __post_init__(self) -> None:
-        if self.qk_layout not in ("adjacent", "half_split"):
-            raise ValueError(f"qk_layout must be 'adjacent' or 'half_split', got {self.qk_layout!r}")
+        for name, layout in (("qk_layout", self.qk_layout), ("v_layout", self.v_layout)):
+            if layout not in ("adjacent", "half_split"):
+                raise ValueError(f"{name} must be 'adjacent' or 'half_split', got {layout!r}")
         if self.n_heads % self.n_kv_heads != 0:
             raise ValueError(
                 f"{self.n_heads} query heads cannot be grouped over "
                 f"{self.n_kv_heads} key/value heads"
             )
-        if self.head_dim % 16 != 0 or not 16 <= self.head_dim <= 256:
-            raise ValueError(
-                f"head size {self.head_dim} is not supported: the attention "
-                "kernels take multiples of 16 from 16 to 256"
-            )
+        for size in (self.head_dim, self.v_head_dim or self.head_dim):
+            if size % 2 != 0 or not 2 <= size <= 256:
+                raise ValueError(
+                    f"head size {size} is not supported: the attention kernels take even "
+                    "sizes up to 256 (padded to a multiple of 16)"
+                )
         if self.window is not None and self.window <= 0:
             raise ValueError(f"attention window must be positive, got {self.window}")
+
+    @property
+    def kernel_head_dim(self) -> int:
+        """The head size the kernels and the cache run with: the larger of the query/key and
+        the value size, rounded up to a multiple of 16.  Heads are padded with zero rows of
+        the projections, which changes no score and no output."""
+        return -(-max(self.head_dim, self.v_head_dim or self.head_dim) // 16) * 16
+
+
+@dataclass(frozen=True)
+class SigmoidAttentionParams(AttentionParams):
+    """Attention whose weights are ``sigmoid(score + gate_h - r1_h ln(1 + r2_h distance))``,
+    not normalised over the keys.  ``gate`` (tensor ``gate``, a number per query head) and
+    ``distance_bias`` (tensors ``r1``, ``r2``) say which of the terms the model has."""
+
+    gate: bool = True
+    distance_bias: bool = True
 
 
 @dataclass(frozen=True)
@@ -89,3 +132,48 @@ class RMSNormParams:
 
     dim: int
     eps: float
+
+
+@dataclass(frozen=True)
+class DenseMLPParams:
+    """Dense feed-forward ``down(act(up x))`` without a gate; ``act`` is ``"gelu_erf"`` (the
+    exact GELU) or ``"gelu_tanh"``."""
+
+    dim: int
+    ffn_dim: int
+    act: str = "gelu_erf"
+
+    def __post_init__(self) -> None:
+        if self.act not in ("gelu_erf", "gelu_tanh"):
+            raise ValueError(f"unknown activation {self.act!r}")
+
+
+@dataclass(frozen=True)
+class DynamicTanhParams:
+    """``tanh(alpha x) * w + b`` with a scalar ``alpha``: a norm that computes no statistics."""
+
+    dim: int
+
+
+@dataclass(frozen=True)
+class TableEmbeddingParams:
+    """``x = table[token]``."""
+
+    vocab_size: int
+    dim: int
+
+
+@dataclass(frozen=True)
+class BigramHashParams:
+    """``x = table[token] + bigram[(previous * mul_prev + token * mul_cur) mod buckets]``; the
+    bigram table has ``buckets + 1`` rows and a sequence's first token takes the last one."""
+
+    vocab_size: int
+    dim: int
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+    def __post_init__(self) -> None:
+        if self.buckets <= 0:
+            raise ValueError(f"a bigram table needs at least one bucket, got {self.buckets}")

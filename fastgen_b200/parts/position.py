@@ -21,9 +21,11 @@ def rope_frequencies(params: RopeParams) -> torch.Tensor:
     and shorter wavelengths are kept (fastgen/forward.py:609-635).  All
     arithmetic is float32 tensor arithmetic, as there.
     """
-    hd = params.head_dim
+    hd = params.rot_dims or params.head_dim
     pows = torch.arange(0, hd, 2, dtype=torch.float32) / hd
     freqs = 1.0 / (params.theta ** pows)
+    if params.linear_factor is not None:
+        freqs = freqs / params.linear_factor
     sc = params.scaling
     if sc is None:
         return freqs
@@ -51,7 +53,12 @@ class Rope(PositionEncoding):
 
     def table(self, device) -> Optional[torch.Tensor]:
         if self._table is None or self._table.device != torch.device(device):
-            self._table = rope_frequencies(self.params).to(device).contiguous()
+            freqs = rope_frequencies(self.params)
+            # pairs that do not turn have frequency zero
+            pairs = self.params.head_dim // 2
+            if freqs.numel() < pairs:
+                freqs = torch.cat([freqs, torch.zeros(pairs - freqs.numel(), dtype=torch.float32)])
+            self._table = freqs.to(device).contiguous()
         return self._table
 
 

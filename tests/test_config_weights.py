@@ -51,7 +51,7 @@ def test_unknown_architecture_and_bad_sizes():
     with pytest.raises(ConfigError, match="FooForCausalLM"):
         model_args_from_config(dict(H.TINY_A, architectures=["FooForCausalLM"]))
     with pytest.raises(ConfigError, match="head size"):
-        model_args_from_config(dict(H.TINY_A, head_dim=24))
+        model_args_from_config(dict(H.TINY_A, head_dim=25))  # odd: no pairs to rotate
     with pytest.raises(ConfigError, match="grouped"):
         model_args_from_config(dict(H.TINY_A, num_key_value_heads=3))
     with pytest.raises(ConfigError, match="positive"):
