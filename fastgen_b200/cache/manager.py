@@ -350,6 +350,10 @@ class CacheManager:
                 for lp in gone:
                     grp.host_table[req.slot, lp] = -1
                     grp.dirty.append((req.slot, lp, -1))
+                if not req.pages[gi]:
+                    # a window shorter than a page can leave a group without a page at a page's
+                    # edge: the bound says nothing then, the next reservation looks at the maps
+                    req.reserved = 0
 
     def release(self, request_id) -> None:
         """The request ended (or is preempted): give everything back."""

@@ -162,7 +162,7 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
   const int hpb = group < PREFILL_ROWS ? group : PREFILL_ROWS;
   dim3 grid(n_tiles, n_kv_heads, (group + hpb - 1) / hpb);
   constexpr size_t smem = prefill_smem_bytes<FG_HEAD_DIM>();
-  auto kern = attention_prefill_kernel<FG_HEAD_DIM>;
+  auto kern = attention_prefill_kernel<FG_HEAD_DIM, false>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -172,8 +172,45 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
   kern<<<grid, THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-      tile_ntok, n_kv_heads, group, hpb, window, scale * 1.4426950408889634f, status);
+      tile_ntok, n_kv_heads, group, hpb, window, scale * 1.4426950408889634f, status, nullptr, nullptr, nullptr);
   FG_CHECK_LAUNCH("fg_attention_prefill_bf16");
+  return 0;
+}
+
+// Prompt portions of the sigmoid-weighted attention on the tensor cores: the tiling of
+// fg_attention_prefill_bf16, the weights of attention_sigmoid.cuh.
+extern "C" int fg_attention_sigmoid_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                                 const void* k_pages, const void* v_pages, const int* block_table,
+                                                 int table_width, int page_size, int n_pages, const int* pos,
+                                                 const int* tile_req, const int* tile_tok0, const int* tile_ntok,
+                                                 int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
+                                                 float scale, const float* gate, const float* r1, const float* r2,
+                                                 int* status, cudaStream_t stream) {
+  using namespace fg_mma;
+  if (n_tiles == 0) return 0;
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_sigmoid_prefill_bf16: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
+               "fg_attention_sigmoid_prefill_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
+  FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0,
+               "fg_attention_sigmoid_prefill_bf16: queries must be 16-byte aligned with a row stride multiple of 8");
+  FG_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "fg_attention_sigmoid_prefill_bf16: r1 and r2 come together");
+  const int group = n_heads / n_kv_heads;
+  const int hpb = group < PREFILL_ROWS ? group : PREFILL_ROWS;
+  dim3 grid(n_tiles, n_kv_heads, (group + hpb - 1) / hpb);
+  constexpr size_t smem = prefill_smem_bytes<FG_HEAD_DIM>();
+  auto kern = attention_prefill_kernel<FG_HEAD_DIM, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_sigmoid_prefill_bf16: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  kern<<<grid, THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
+      (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
+      tile_ntok, n_kv_heads, group, hpb, window, scale, status, gate, r1, r2);
+  FG_CHECK_LAUNCH("fg_attention_sigmoid_prefill_bf16");
   return 0;
 }
 

@@ -207,7 +207,11 @@ constexpr size_t prefill_smem_bytes() {
   return sizeof(__nv_bfloat16) * Tile<HD>::LD * (PREFILL_ROWS + 4 * PREFILL_KEYS);
 }
 
-template <int HD>
+// With SIGMOID the weight of a visible key is sigmoid(q.k * scale + gate_h - r1_h ln(1 + r2_h (i - j)))
+// (gate, r1, r2: float32 per query head, each may be null), not normalised over the keys: no running
+// maximum, no rescaling, no division at the end; scale_log2 is then the plain scale.  The weights are
+// rounded to bfloat16 for the second product as the probabilities are.
+template <int HD, bool SIGMOID = false>
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                          int out_stride, const __nv_bfloat16* __restrict__ k_pages,
@@ -215,7 +219,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          int table_width, int page_size, int n_pages, const int* __restrict__ pos,
                          const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
                          const int* __restrict__ tile_ntok, int n_kv_heads, int group, int heads_per_block,
-                         int window, float scale_log2, int* status) {
+                         int window, float scale_log2, int* status, const float* __restrict__ gate,
+                         const float* __restrict__ dist_r1, const float* __restrict__ dist_r2) {
   constexpr int LD = Tile<HD>::LD;
   constexpr int NT = PREFILL_KEYS / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -301,6 +306,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // the heads' numbers of this thread's two rows (sigmoid weights only)
+  float gate_r[2] = {0.f, 0.f}, r1_r[2] = {0.f, 0.f}, r2_r[2] = {0.f, 0.f};
+  if (SIGMOID) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int head = g * group + min(row_head(h ? r1 : r0), group - 1);
+      if (gate != nullptr) gate_r[h] = gate[head];
+      if (dist_r1 != nullptr) r1_r[h] = dist_r1[head];
+      if (dist_r2 != nullptr) r2_r[h] = dist_r2[head];
+    }
+  }
 
   for (int t = 0; t < n_tiles; ++t) {
     if (t + 1 < n_tiles) {
@@ -325,10 +341,20 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
           const int j = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
           const int p = (e < 2) ? p0 : p1;
           const bool vis = p >= 0 && j <= p && (window <= 0 || j > p - window);
-          s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
+          if (SIGMOID) {
+            float wgt = 0.f;
+            if (vis) {
+              float z = s[nt][e] * scale_log2 + gate_r[e >> 1];
+              if (dist_r1 != nullptr) z -= r1_r[e >> 1] * logf(1.f + r2_r[e >> 1] * (float)(p - j));
+              wgt = __bfloat162float(__float2bfloat16_rn(1.f / (1.f + expf(-z))));
+            }
+            s[nt][e] = wgt;
+          } else {
+            s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
+          }
         }
       }
-      softmax_step<HD, NT>(s, o, m, l);
+      if (!SIGMOID) softmax_step<HD, NT>(s, o, m, l);
       pv_product<HD, NT>(o, s, vs, lane);
     }
     __syncthreads();  // everyone is done with this stage before it is refilled
@@ -339,7 +365,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   for (int h = 0; h < 2; ++h) {
     const int r = h ? r1 : r0;
     if (!row_valid(r)) continue;
-    const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+    const float inv = SIGMOID ? 1.f : (l[h] > 0.f ? 1.f / l[h] : 0.f);
     __nv_bfloat16* dst = out + (size_t)(tok0 + row_token(r)) * out_stride + (g * group + row_head(r)) * HD;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {

@@ -14,6 +14,10 @@
 // so a row's result does not depend on how the prompt was cut or what else is in the batch.
 //
 // Storage type T (float or bf16) only affects loads and the final store.
+//
+// With tile_ntok == nullptr the list is one of single tokens (tile i is token tile_tok0[i] of
+// request tile_req[i]); an entry without a request (negative) is then skipped, where a tile
+// list's padding tile has its output rows zeroed.
 #pragma once
 
 #include "attention_simt.cuh"
@@ -44,7 +48,7 @@ attention_sigmoid_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   const int sub = blockIdx.z;      // which slice of the group's heads
   const int b = tile_req[tile];
   const int tok0 = tile_tok0[tile];
-  const int ntok = tile_ntok[tile];
+  const int ntok = tile_ntok != nullptr ? tile_ntok[tile] : 1;
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
 
@@ -53,6 +57,7 @@ attention_sigmoid_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
 
   if (b < 0) {
+    if (tile_ntok == nullptr) return;
     for (int i = tid; i < ROWS * HD; i += THREADS) {
       const int r = i / HD, d = i - r * HD;
       if (row_valid(r))

@@ -64,6 +64,8 @@ _ATTN_SIGNATURES = {
     "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_attention_sigmoid": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                              _P, _P, _P, _P, _P],
+    "fg_attention_sigmoid_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                                          _F, _P, _P, _P, _P, _P],
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
                                  ctypes.c_longlong, _I, _P, _P],
@@ -580,19 +582,36 @@ class Ops:
                           window: Optional[int], scale: float, gate=None, r1=None, r2=None) -> None:
         """Paged attention with sigmoid weights, not normalised over the keys:
         ``sum_j sigmoid(q.k_j * scale + gate[h] - r1[h] * ln(1 + r2[h] * distance)) v_j`` over the
-        visible keys; ``gate``, ``r1``, ``r2`` are float32 [heads] or ``None``.  One CUDA-core kernel
-        with float32 arithmetic serves both storage types, prompt portions and single tokens."""
+        visible keys; ``gate``, ``r1``, ``r2`` are float32 [heads] or ``None``.  float32: one
+        CUDA-core kernel for all tokens.  bfloat16: prompt portions on the tensor cores
+        (``mma.sync``, the weights rounded to bfloat16 for the second product), single tokens on
+        the CUDA-core kernel, which reads a window's keys once."""
         lib = attn(head_dim)
         k_pages, v_pages, block_table = memory.k_pages, memory.v_pages, memory.block_table
         assert q.stride(1) == 1 and out.stride(1) == 1
         for t in (gate, r1, r2):
             assert t is None or (t.dtype == torch.float32 and t.numel() == n_heads and t.is_contiguous())
-        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, SIMT_ROWS), 1)
-        _check(lib, lib.fg_attention_sigmoid(
-            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), _ptr(k_pages), _ptr(v_pages),
-            _ptr(block_table), block_table.shape[1], memory.page_size, k_pages.shape[0], _ptr(ctx.pos),
-            _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim,
-            int(window or 0), float(scale), _ptr(gate), _ptr(r1), _ptr(r2), _ptr(self.status), _stream()))
+        head = (_ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], memory.page_size,
+                k_pages.shape[0], _ptr(ctx.pos))
+        tail = (n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(gate), _ptr(r1), _ptr(r2),
+                _ptr(self.status), _stream())
+        if q.dtype == torch.float32:
+            tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, SIMT_ROWS), 1)
+            _check(lib, lib.fg_attention_sigmoid(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), FG_F32, *head,
+                _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, *tail))
+            return
+        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, PREFILL_ROWS), 2)
+        if tiles.n:
+            _check(lib, lib.fg_attention_sigmoid_prefill_bf16(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), *head,
+                _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, *tail))
+        singles = ctx.single_tokens()
+        if singles.n:
+            # a list of single tokens: no token counts
+            _check(lib, lib.fg_attention_sigmoid(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), FG_BF16, *head,
+                _ptr(singles.req), _ptr(singles.tok), None, singles.n, *tail))
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,
                out_tokens, out_logprobs=None, scratch=None, with_status: bool = False) -> torch.Tensor:

@@ -142,7 +142,8 @@ class Fastgen:
 
         # pages: from max_seq, or from the memory budget (generate.py:206-236)
         per_token = model.cache_bytes_per_token(act_bytes)
-        widest = max((getattr(l.ffn.params, "ffn_dim", model.args.dim) for l in model.args.layers))
+        widest = max((getattr(l.ffn.params, "ffn_dim", model.args.dim) if l.ffn is not None else model.args.dim
+                      for l in model.args.layers))
         mp = mem_params(model.weight_bytes(), per_token, model.args.dim, widest, act_bytes,
                         max(args.prefill_gb, 0.1), args.gpu_gb)
         mp.round_to(block)

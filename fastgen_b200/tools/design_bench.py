@@ -1,0 +1,299 @@
+"""Throughput of one design beside another at equal size, step by step and kernel by kernel.
+
+``bench.py --design sinorax`` runs this: prefill and decode throughput of a Sinorax model at a
+few sizes that resemble a real model's layers (random weights), beside a Llama-shaped model of
+the same width, heads, head size, number of layers and number of parameters a layer, and the
+time of each kernel family of the two designs at those sizes with its fraction of the roofline
+(HBM bandwidth for the elementwise kernels and single-token attention, tensor throughput for
+prompt attention).  Timed with CUDA events, L2 flushed before every timed launch.
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Callable, Dict, List
+
+import torch
+
+PAGE = 64
+PREFILL_TOKENS = 2048
+DECODE_BATCH = 8
+DECODE_CONTEXT = 2048
+SEED = 4
+
+#: name -> (width, layers, query heads, key/value heads, head size, SwiGLU width, vocabulary, window)
+SIZES = {
+    "1b-like": (2048, 6, 32, 8, 64, 8192, 128256, 1024),
+    "3b-like": (3072, 6, 24, 8, 128, 8192, 128256, 1024),
+}
+
+
+def llama_config(width, layers, heads, kv, head_dim, ffn, vocab, window=None) -> dict:
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=width, intermediate_size=ffn, num_hidden_layers=layers,
+               num_attention_heads=heads, num_key_value_heads=kv, head_dim=head_dim, rms_norm_eps=1e-5, vocab_size=vocab,
+               tie_word_embeddings=False, rope_theta=500000.0, max_position_embeddings=131072)
+    if window:
+        cfg["sliding_window"] = window
+    return cfg
+
+
+def sinorax_config(width, layers, heads, kv, head_dim, ffn, vocab, window, kinds=("attention", "attention", "attention_2")) -> dict:
+    """Two softmax layers, then one with sigmoid weights and a window, and so on; the dense
+    feed-forward is half as wide again as the gated one, which gives a layer the same number
+    of parameters."""
+    out = []
+    for i in range(layers):
+        kind = kinds[i % len(kinds)]
+        mixer = dict(heads=heads, kv_heads=kv, dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5)
+        if kind == "attention":
+            mixer["rot"] = dict(dims=head_dim, base=500000.0, scaling=dict(factor=2.0))
+        else:
+            mixer["mask"] = dict(size=window)
+        out.append(dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=ffn * 3 // 2)))
+    return dict(architecture="Sinorax", vocab=vocab, width=width, norm=dict(eps=1e-5), logit_scale=1.0, logit_softcap=30.0,
+                embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)), layers=out)
+
+
+class Timer:
+    """CUDA-event times of single launches, each after a write larger than L2."""
+
+    def __init__(self, device) -> None:
+        self.flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=device)  # 256 MB
+
+    def us(self, fn: Callable[[], None], reps: int = 7) -> float:
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        times.sort()
+        return times[len(times) // 2]
+
+
+def _engine(cfg, device, max_requests, tokens):
+    from ..config import model_args_from_config
+    from ..engine import Engine, Model
+
+    model = Model.random(model_args_from_config(cfg), torch.bfloat16, device, seed=SEED)
+    n_pages = max_requests * (-(-(tokens + 1) // PAGE)) + 2
+    return Engine(model, page_size=PAGE, n_pages=n_pages, max_requests=max_requests, max_length=tokens + PAGE,
+                  num_cuda_graphs=max_requests, max_step_tokens=PREFILL_TOKENS)
+
+
+def _fill(engine) -> None:
+    for grp in engine.cache.groups:
+        grp.k_pages.normal_(0.0, 1.0)
+        grp.v_pages.normal_(0.0, 1.0)
+
+
+def model_throughput(cfg, device) -> Dict[str, float]:
+    """Prefill tokens/s of one 2,048-token prompt and decode tokens/s at batch 8 around position
+    2,048, through the engine's step function (graphs included), device-timed."""
+    from ..csrc.ops import Ops
+    from ..engine import StepEntry
+    from ..sampling import Sampler
+
+    engine = _engine(cfg, device, DECODE_BATCH, max(PREFILL_TOKENS, DECODE_CONTEXT))
+    vocab = engine.model.args.vocab_size
+    gen = torch.Generator().manual_seed(SEED)
+    toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+
+    def prefill_once():
+        engine.admit("p")
+        engine.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])])
+        engine.release("p")
+
+    for _ in range(3):
+        prefill_once()
+    times = []
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        prefill_once()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    pre_ms = min(times)
+
+    steps, warm = 64, 5
+    ids = [f"d{i}" for i in range(DECODE_BATCH)]
+    for rid in ids:
+        r = engine.admit(rid)
+        engine.cache.reserve(r, DECODE_CONTEXT - steps - warm)
+        engine.cache.advance(r, DECODE_CONTEXT - steps - warm)
+    _fill(engine)
+    reqs = [engine.cache.get(rid) for rid in ids]
+    slots = [r.slot for r in reqs]
+    sampler = Sampler(engine.ops, vocab, DECODE_BATCH, use_sampling=False)
+    tokens = torch.randint(0, vocab, (DECODE_BATCH,), generator=gen).to(device, torch.int32)
+
+    def one_step():
+        nonlocal tokens
+        for r in reqs:
+            engine.cache.reserve(r, r.length + 1)
+        engine.cache.flush_tables()
+        logits = engine.graphs.run(tokens, [r.length for r in reqs], slots)
+        tokens, _ = sampler.sample(logits, [0.0] * DECODE_BATCH, [0] * DECODE_BATCH, [0] * DECODE_BATCH)
+        for r in reqs:
+            engine.cache.advance(r, r.length + 1)
+
+    for _ in range(warm):
+        one_step()
+    torch.cuda.synchronize()
+    launches = Ops.launches
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        one_step()
+    b.record()
+    torch.cuda.synchronize()
+    dec_ms = a.elapsed_time(b) / steps
+    launches = (Ops.launches - launches) // steps
+    engine.ops.check_status()
+    weight_bytes = engine.model.weight_bytes()
+    out = dict(prefill_tok_s=round(PREFILL_TOKENS / pre_ms * 1e3, 1), prefill_ms=round(pre_ms, 3),
+               decode_tok_s=round(DECODE_BATCH / dec_ms * 1e3, 1), decode_ms_per_step=round(dec_ms, 4),
+               decode_launches_per_step=int(launches), weight_gb=round(weight_bytes / 1e9, 3),
+               decode_weight_stream_gbs=round(weight_bytes / (dec_ms * 1e-3) / 1e9, 1))
+    for rid in ids:
+        engine.release(rid)
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def _attention_times(cfg, device, timer: Timer, layer: int, flops_window, heads, kv, head_dim) -> Dict[str, float]:
+    """The attention launches of one layer alone: a 2,048-token prompt, and 8 single tokens at
+    position 2,048, with what the mixer adds around them (turning the outputs back)."""
+    from ..engine import StepEntry
+
+    engine = _engine(cfg, device, DECODE_BATCH, DECODE_CONTEXT)
+    _fill(engine)
+    mixer = engine.model.blocks[layer].mixer
+    memory = engine.memories[layer]
+    out = {}
+    gen = torch.Generator().manual_seed(SEED)
+
+    def context(entries):
+        reqs = engine._validate(entries)
+        for e, r in zip(entries, reqs):
+            engine.cache.reserve(r, r.length + len(e.tokens))
+        engine.cache.flush_tables()
+        return engine.build_context(entries, reqs)
+
+    # the prompt
+    engine.admit("p")
+    ctx = context([StepEntry("p", [1] * PREFILL_TOKENS, [])])
+    q = torch.randn(PREFILL_TOKENS, mixer.q_width, generator=gen).to(device, torch.bfloat16)
+    o = torch.empty_like(q)
+    us = timer.us(lambda: mixer._attend(q, o, ctx, memory))
+    w = flops_window or PREFILL_TOKENS
+    keys = sum(min(i + 1, w) for i in range(PREFILL_TOKENS))
+    out["prefill_us"] = round(us, 1)
+    out["prefill_tflops"] = round(4 * head_dim * heads * keys / (us * 1e-6) / 1e12, 1)
+    if getattr(mixer, "v_unfreqs", None) is not None:
+        out["prefill_unrotate_us"] = round(timer.us(lambda: engine.ops.rotate_heads(
+            o, ctx.pos, ctx.req, mixer.v_unfreqs, heads, head_dim)), 1)
+    engine.release("p")
+    # single tokens
+    ids = [f"d{i}" for i in range(DECODE_BATCH)]
+    for rid in ids:
+        r = engine.admit(rid)
+        engine.cache.reserve(r, DECODE_CONTEXT - 1)
+        engine.cache.advance(r, DECODE_CONTEXT - 1)
+    ctx = context([StepEntry(rid, [1], []) for rid in ids])
+    q = torch.randn(DECODE_BATCH, mixer.q_width, generator=gen).to(device, torch.bfloat16)
+    o = torch.empty_like(q)
+    us = timer.us(lambda: mixer._attend(q, o, ctx, memory))
+    keys = min(DECODE_CONTEXT, flops_window or DECODE_CONTEXT)
+    out["decode_us"] = round(us, 1)
+    out["decode_gbs"] = round(DECODE_BATCH * keys * 2 * kv * head_dim * 2 / (us * 1e-6) / 1e9, 1)
+    if getattr(mixer, "v_unfreqs", None) is not None:
+        out["decode_unrotate_us"] = round(timer.us(lambda: engine.ops.rotate_heads(
+            o, ctx.pos, ctx.req, mixer.v_unfreqs, heads, head_dim)), 1)
+    engine.ops.check_status()
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def kernel_table(size, device, peaks) -> Dict[str, dict]:
+    """Every kernel family of the two designs alone at one size: microseconds and the fraction
+    of the roofline (bytes or FLOPs that the operation needs over the measured peak)."""
+    from ..csrc.ops import Ops
+
+    width, _layers, heads, kv, head_dim, ffn, vocab, window = size
+    ops = Ops(torch.bfloat16, device)
+    timer = Timer(device)
+    gen = torch.Generator().manual_seed(SEED)
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    table: Dict[str, dict] = {}
+
+    def bw(name, us, nbytes):
+        table[name] = dict(us=round(us, 1), gbs=round(nbytes / (us * 1e-6) / 1e9, 1), hbm_frac=round(nbytes / (us * 1e-6) / hbm, 3))
+
+    def rand(*shape, dtype=torch.bfloat16):
+        return torch.randn(*shape, generator=gen).to(device, dtype)
+
+    for t in (PREFILL_TOKENS, DECODE_BATCH):
+        h, delta = rand(t, width, dtype=torch.float32), rand(t, width)
+        out = torch.empty(t, width, dtype=torch.bfloat16, device=device)
+        w32 = [rand(1, dtype=torch.float32), rand(width, dtype=torch.float32), rand(width, dtype=torch.float32)]
+        nbytes = t * width * (4 + 4 + 2 + 2)
+        bw(f"norm+sum t={t}: dynamic tanh (post, sum, pre)", timer.us(lambda: ops.dyt(h, w32, out, delta=delta, post=w32)), nbytes)
+        wb = rand(width)
+        bw(f"norm+sum t={t}: rmsnorm (sum, norm)", timer.us(lambda: ops.rmsnorm(h, wb, 1e-5, out=out, delta=delta)), nbytes)
+    t = PREFILL_TOKENS
+    x = rand(t, ffn * 3 // 2)
+    bw(f"activation t={t}: gelu in place [t, 1.5 f]", timer.us(lambda: ops.bias_act(x, "gelu_erf")), t * (ffn * 3 // 2) * 4)
+    x13, g = rand(t, 2 * ffn), torch.empty(t, ffn, dtype=torch.bfloat16, device=device)
+    bw(f"activation t={t}: silu gate [t, 2 f] -> [t, f]", timer.us(lambda: ops.silu_gate(x13, g, 8)), t * ffn * 6)
+    logits = rand(DECODE_BATCH, vocab, dtype=torch.float32)
+    bw("logits scale and cap, 8 rows", timer.us(lambda: ops.scale_softcap(logits, 1.0, 30.0)), DECODE_BATCH * vocab * 8)
+
+    geometry = (heads, kv, head_dim)
+    small = (width, 3, heads, kv, head_dim, ffn, 1024)  # the attention launches do not depend on depth or vocabulary
+    sx = sinorax_config(*small, window)
+    table["attention softmax (sinorax 'attention', causal)"] = _attention_times(sx, device, timer, 0, None, *geometry)
+    table["attention softmax (llama, causal)"] = _attention_times(llama_config(*small), device, timer, 0, None, *geometry)
+    table[f"attention sigmoid (sinorax 'attention_2', window {window})"] = _attention_times(sx, device, timer, 2, window, *geometry)
+    table[f"attention softmax (llama, window {window})"] = _attention_times(llama_config(*small, window=window), device, timer, 0,
+                                                                          window, *geometry)
+    for name, row in table.items():
+        if "prefill_tflops" in row:
+            row["prefill_tensor_frac"] = round(row["prefill_tflops"] * 1e12 / tensor, 3)
+            row["decode_hbm_frac"] = round(row["decode_gbs"] * 1e9 / hbm, 3)
+    return table
+
+
+def run(sizes: List[str], peaks: dict, kernels: bool = True) -> dict:
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    out = {"metric": "prefill and decode tokens/s of Sinorax beside a Llama-shaped model of equal size (bf16, random weights)",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+           "config": dict(prefill_tokens=PREFILL_TOKENS, decode_batch=DECODE_BATCH, decode_context=DECODE_CONTEXT, page=PAGE,
+                          l2="flushed before every timed kernel; model steps stream all weights"),
+           "peaks": peaks, "sizes": {}}
+    for name in sizes:
+        size = SIZES[name]
+        entry = dict(width=size[0], layers=size[1], heads=size[2], kv_heads=size[3], head_dim=size[4], swiglu_ffn=size[5],
+                     dense_ffn=size[5] * 3 // 2, vocab=size[6], window=size[7])
+        entry["sinorax"] = model_throughput(sinorax_config(*size), device)
+        entry["llama"] = model_throughput(llama_config(*size[:7]), device)
+        if kernels:
+            entry["kernels"] = kernel_table(size, device, peaks)
+        out["sizes"][name] = entry
+    return out
+
+
+if __name__ == "__main__":
+    print(json.dumps(run(list(SIZES), dict(hbm_gbs=6650.0, bf16_tflops=1590.0))))

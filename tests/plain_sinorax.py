@@ -1,9 +1,9 @@
-"""A plain, slow Sinorax in float32 on the CPU: the oracle of the tests.
+"""A plain, slow Sinorax on the CPU: the oracle of the tests.
 
 One function per mechanism, written from the design's equations and sharing
 no code with the package.  A whole sequence is run at once: no cache, no
 portions, no batches.  ``forward`` takes the parsed ``config.json`` and a dict
-of float32 tensors by checkpoint name.
+of tensors by checkpoint name, and computes in their dtype (float64 in the tests).
 """
 
 from __future__ import annotations
@@ -54,13 +54,56 @@ def rotate_half_pairs(x: torch.Tensor, pos: torch.Tensor, dims: int, base: float
     paired with ``i + dims/2`` and the pair turns by ``sign * pos * base^(-2i/dims) / divide``."""
     half = dims // 2
     i = torch.arange(half, dtype=torch.float32)
-    freq = base ** (-2.0 * i / dims) / divide
-    ang = sign * pos.to(torch.float32)[:, None] * freq[None, :]
+    freq = (base ** (-2.0 * i / dims) / divide).to(x.dtype)  # the table is float32, as the design computes it
+    ang = sign * pos.to(x.dtype)[:, None] * freq[None, :]
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     u, v = x[..., :half], x[..., half:dims]
     out = x.clone()
     out[..., :half] = u * c - v * s
     out[..., half:dims] = v * c + u * s
+    return out
+
+
+def softmax_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: Optional[int] = None,
+                 pos: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[i, h] = sum_j softmax_j(q_i . k_j * scale) v_j`` over the keys ``j`` with ``pos_j <= pos_i``
+    (and ``pos_i - pos_j < window``).  q [T, H, d], k [S, G, d], v [S, G, dv]; ``pos`` gives the
+    queries' positions among the keys (default: query i is key i)."""
+    t, nh, _ = q.shape
+    ng = k.shape[1]
+    pos = torch.arange(t) if pos is None else pos
+    out = torch.zeros(t, nh, v.shape[2], dtype=q.dtype)
+    for head in range(nh):
+        g = head // (nh // ng)
+        for i in range(t):
+            p = int(pos[i])
+            lo = 0 if window is None else max(0, p - window + 1)
+            s = (k[lo : p + 1, g] @ q[i, head]) * scale
+            out[i, head] = torch.softmax(s, dim=0) @ v[lo : p + 1, g]
+    return out
+
+
+def sigmoid_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: Optional[int],
+                 gate: Optional[torch.Tensor], r1: Optional[torch.Tensor], r2: Optional[torch.Tensor],
+                 pos: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[i, h] = sum_j sigmoid(q_i . k_j * scale + gate_h - r1_h ln(1 + r2_h (pos_i - j))) v_j`` over
+    the visible keys; the weights are not normalised."""
+    t, nh, _ = q.shape
+    ng = k.shape[1]
+    pos = torch.arange(t) if pos is None else pos
+    out = torch.zeros(t, nh, v.shape[2], dtype=q.dtype)
+    for head in range(nh):
+        g = head // (nh // ng)
+        for i in range(t):
+            p = int(pos[i])
+            lo = 0 if window is None else max(0, p - window + 1)
+            s = (k[lo : p + 1, g] @ q[i, head]) * scale
+            if r1 is not None:
+                dist = (p - torch.arange(lo, p + 1)).to(q.dtype)
+                s = s - r1[head] * torch.log(1.0 + r2[head] * dist)
+            if gate is not None:
+                s = s + gate[head]
+            out[i, head] = torch.sigmoid(s) @ v[lo : p + 1, g]
     return out
 
 
@@ -80,15 +123,7 @@ def softmax_attention(h: torch.Tensor, m: Mapping, w: Mapping[str, torch.Tensor]
         q = rotate_half_pairs(q, pos, rot["dims"], rot["base"], factor)
         k = rotate_half_pairs(k, pos, rot["dims"], rot["base"], factor)
         v = rotate_half_pairs(v, pos, dv, rot["base"])
-    window = (m.get("mask") or {}).get("size")
-    out = torch.zeros(t, nh, dv)
-    for head in range(nh):
-        g = head // (nh // ng)
-        for i in range(t):
-            lo = 0 if window is None else max(0, i - window + 1)
-            s = (k[lo : i + 1, g] @ q[i, head]) * m["scale"]
-            a = torch.softmax(s, dim=0)
-            out[i, head] = a @ v[lo : i + 1, g]
+    out = softmax_core(q, k, v, m["scale"], (m.get("mask") or {}).get("size"))
     if rot:
         out = rotate_half_pairs(out, pos, dv, rot["base"], sign=-1.0)
     return out.reshape(t, nh * dv) @ w[p + "o"].T + w[p + "o.b"]
@@ -102,21 +137,34 @@ def sigmoid_attention(h: torch.Tensor, m: Mapping, w: Mapping[str, torch.Tensor]
     q = (h @ w[p + "q"].T).view(t, nh, d)
     k = (h @ w[p + "k"].T).view(t, ng, d)
     v = (h @ w[p + "v"].T).view(t, ng, dv)
-    window = (m.get("mask") or {}).get("size")
-    out = torch.zeros(t, nh, dv)
-    for head in range(nh):
-        g = head // (nh // ng)
-        r1, r2, pb = w[p + "r1"][head], w[p + "r2"][head], w[p + "pb"][head]
-        for i in range(t):
-            lo = 0 if window is None else max(0, i - window + 1)
-            dist = (i - torch.arange(lo, i + 1)).to(torch.float32)
-            s = (k[lo : i + 1, g] @ q[i, head]) * m["scale"] - r1 * torch.log(1.0 + r2 * dist)
-            a = torch.sigmoid(s + pb)
-            out[i, head] = a @ v[lo : i + 1, g]
+    out = sigmoid_core(q, k, v, m["scale"], (m.get("mask") or {}).get("size"), w[p + "pb"], w[p + "r1"], w[p + "r2"])
     return out.reshape(t, nh * dv) @ w[p + "o"].T
 
 
 MIXERS = {"attention": softmax_attention, "attention_2": sigmoid_attention}
+
+
+def read_model(model_dir, dtype=torch.float64):
+    """``(config, tensors)`` of a model folder, the tensors in ``dtype``."""
+    import json
+    from pathlib import Path
+
+    from safetensors import safe_open
+
+    with open(Path(model_dir) / "config.json") as f:
+        cfg = json.load(f)
+    w = {}
+    with safe_open(str(Path(model_dir) / "model.safetensors"), "pt") as f:
+        for key in f.keys():
+            w[key] = f.get_tensor(key).to(dtype)
+    return cfg, w
+
+
+def greedy(cfg: Mapping, w: Mapping[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(int(forward(cfg, w, seq)[-1].argmax()))
+    return seq[len(prompt):]
 
 
 def forward(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None) -> torch.Tensor:

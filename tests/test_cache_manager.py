@@ -167,3 +167,19 @@ def test_groups_with_pages_of_their_own_and_one_pool():
     assert m.free_pages() == [6, 12, 24]
     with pytest.raises(ValueError):
         CacheSpec(1, 8, None, n_pools=3)
+
+
+def test_a_window_shorter_than_a_page_may_leave_a_group_without_pages():
+    """A window of one key: at a page's edge the windowed group holds nothing, the bookkeeping
+    stays consistent and the next token gets its page."""
+    m = CacheManager([CacheSpec(1, 16), CacheSpec(1, 16, 1)], [None, None], [None, None], page_size=4, n_pages=8,
+                     max_requests=2, max_length=32)
+    r = m.admit("a")
+    for length in range(1, 14):
+        m.reserve(r, length)
+        m.advance(r, length)
+        m.check()
+        assert len(r.pages[1]) <= 1
+    m.release("a")
+    m.check()
+    assert m.free_pages() == [8, 8]
