@@ -108,6 +108,40 @@ extern "C" int fg_attention_sigmoid(const void* q, int q_stride, void* out, int 
   return 0;
 }
 
+// Single tokens of the sigmoid-weighted attention in bfloat16: token seq_tok[i] of request
+// seq_req[i] (negative: padding, skipped).
+extern "C" int fg_attention_sigmoid_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                                const void* k_pages, const void* v_pages, const int* block_table,
+                                                int table_width, int page_size, int n_pages, const int* pos,
+                                                const int* seq_req, const int* seq_tok, int n_seqs, int n_heads,
+                                                int n_kv_heads, int head_dim, int window, float scale,
+                                                const float* gate, const float* r1, const float* r2, int* status,
+                                                cudaStream_t stream) {
+  using namespace fg_attn;
+  if (n_seqs == 0) return 0;
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_sigmoid_decode_bf16: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
+               "fg_attention_sigmoid_decode_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
+  FG_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "fg_attention_sigmoid_decode_bf16: r1 and r2 come together");
+  FG_CHECK_ARG(((uintptr_t)k_pages & 15) == 0, "fg_attention_sigmoid_decode_bf16: the key pool must be 16-byte aligned");
+  dim3 grid(n_seqs, n_kv_heads);
+  constexpr size_t smem = sigmoid_decode_smem_bytes<FG_HEAD_DIM>();
+  auto kern = attention_sigmoid_decode_kernel<FG_HEAD_DIM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_sigmoid_decode_bf16: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  kern<<<grid, SIG_DECODE_KEYS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
+      (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_kv_heads,
+      n_heads / n_kv_heads, window, scale, gate, r1, r2, status);
+  FG_CHECK_LAUNCH("fg_attention_sigmoid_decode_bf16");
+  return 0;
+}
+
 // ---------------------------------------------------------------------------------
 // bfloat16 on the tensor cores
 // ---------------------------------------------------------------------------------
@@ -491,8 +525,58 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
   (split ? kern_parts : kern_whole)<<<grid, fg_tc5::THREADS, smem, stream>>>(
       km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, block_table, table_width,
       page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
-      scale * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, split_slots, real_tiles, status);
+      scale * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, split_slots, real_tiles, status,
+      nullptr, nullptr, nullptr);
   FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
+  return 0;
+}
+
+// Prompt portions of the sigmoid-weighted attention on tcgen05 / TMEM: the kernel, tiling and
+// work counter of fg_attention_prefill_tc5_bf16 with the weights of attention_sigmoid.cuh; items
+// are never split (a window keeps them short).
+extern "C" int fg_attention_sigmoid_prefill_tc5_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                                     const void* k_map, const void* v_map, int layer,
+                                                     const int* block_table, int table_width, int page_size,
+                                                     int n_pages, const int* pos, const int* tile_req,
+                                                     const int* tile_tok0, const int* tile_ntok, int n_tiles,
+                                                     int n_heads, int n_kv_heads, int head_dim, int window,
+                                                     float scale, const float* gate, const float* r1, const float* r2,
+                                                     unsigned int* work_counter, const int* real_tiles, int* status,
+                                                     cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  FG_CHECK_ARG(work_counter != nullptr, "fg_attention_sigmoid_prefill_tc5_bf16: no work counter");
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_sigmoid_prefill_tc5_bf16: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
+               "fg_attention_sigmoid_prefill_tc5_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
+  FG_CHECK_ARG(page_size >= 8 && (page_size & (page_size - 1)) == 0,
+               "fg_attention_sigmoid_prefill_tc5_bf16: pages of %d slots are not supported", page_size);
+  FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0,
+               "fg_attention_sigmoid_prefill_tc5_bf16: queries and outputs must be 16-byte aligned with strides "
+               "multiple of 8");
+  FG_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "fg_attention_sigmoid_prefill_tc5_bf16: r1 and r2 come together");
+  const int group = n_heads / n_kv_heads;
+  const int hpb = group < fg_tc5::ROWS ? group : fg_tc5::ROWS;
+  CUtensorMap km, vm;
+  memcpy(&km, k_map, sizeof(CUtensorMap));
+  memcpy(&vm, v_map, sizeof(CUtensorMap));
+  constexpr size_t smem = fg_tc5::smem_bytes<FG_HEAD_DIM>();
+  auto kern = fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, false, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_sigmoid_prefill_tc5_bf16: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const long long items = tc5_items(n_tiles, n_heads, n_kv_heads);
+  FG_CHECK_ARG(items < (1ll << 30), "fg_attention_sigmoid_prefill_tc5_bf16: %lld work items in one call", items);
+  const long long resident = 2ll * sm_count();
+  const int grid = (int)(items < resident ? items : resident);
+  kern<<<grid, fg_tc5::THREADS, smem, stream>>>(
+      km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, block_table, table_width,
+      page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
+      scale * 1.4426950408889634f, work_counter, 1, nullptr, nullptr, 0, real_tiles, status, gate, r1, r2);
+  FG_CHECK_LAUNCH("fg_attention_sigmoid_prefill_tc5_bf16");
   return 0;
 }
 #else

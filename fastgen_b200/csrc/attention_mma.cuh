@@ -345,8 +345,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             float wgt = 0.f;
             if (vis) {
               float z = s[nt][e] * scale_log2 + gate_r[e >> 1];
-              if (dist_r1 != nullptr) z -= r1_r[e >> 1] * logf(1.f + r2_r[e >> 1] * (float)(p - j));
-              wgt = __bfloat162float(__float2bfloat16_rn(1.f / (1.f + expf(-z))));
+              // the special-function unit's logarithm, exponential and reciprocal: a few units in the
+              // last place of float32, far below the bfloat16 rounding of the weight that follows
+              if (dist_r1 != nullptr) z -= r1_r[e >> 1] * __logf(1.f + r2_r[e >> 1] * (float)(p - j));
+              wgt = __bfloat162float(__float2bfloat16_rn(__fdividef(1.f, 1.f + __expf(-z))));
             }
             s[nt][e] = wgt;
           } else {

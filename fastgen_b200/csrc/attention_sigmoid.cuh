@@ -171,4 +171,141 @@ attention_sigmoid_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------------------------
+// Single tokens, bfloat16: one block per (token, key/value head) walks the token's visible keys
+// in stretches of SIG_DECODE_KEYS positions that start at multiples of that number.  A thread
+// takes one key of the stretch: it reads the key's row and the value's row with 16-byte loads
+// (all of a stretch's loads are in flight together: one round trip to memory a stretch), leaves
+// the value in shared memory, forms the scores of the group's heads (float32, dimensions in
+// ascending order) and leaves the weights in shared memory; then the threads turn to the
+// output: thread (part, d) adds up weight * value over its part of the stretch's keys for
+// dimension d, the parts are added in ascending order at the end.  Nothing is normalised, so
+// there are no partial maxima and no merge: a token's result depends on its own position and
+// window only.  Groups of more than SIG_DECODE_HEADS heads take passes.
+// ---------------------------------------------------------------------------------
+constexpr int SIG_DECODE_KEYS = 256;   // = threads
+constexpr int SIG_DECODE_HEADS = 8;
+
+template <int HD>
+constexpr size_t sigmoid_decode_smem_bytes() {
+  return sizeof(__nv_bfloat16) * SIG_DECODE_KEYS * HD;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(SIG_DECODE_KEYS)
+attention_sigmoid_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
+                                int out_stride, const __nv_bfloat16* __restrict__ k_pages,
+                                const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
+                                int table_width, int page_size, int n_pages, const int* __restrict__ pos,
+                                const int* __restrict__ seq_req, const int* __restrict__ seq_tok, int n_kv_heads,
+                                int group, int window, float scale, const float* __restrict__ gate,
+                                const float* __restrict__ r1, const float* __restrict__ r2, int* status) {
+  constexpr int PARTS = SIG_DECODE_KEYS / HD;                    // threads side by side on one dimension
+  constexpr int PART_KEYS = (SIG_DECODE_KEYS + PARTS - 1) / PARTS;
+  extern __shared__ __align__(16) unsigned char sig_smem[];
+  __nv_bfloat16(*v_s)[HD] = reinterpret_cast<__nv_bfloat16(*)[HD]>(sig_smem);  // [SIG_DECODE_KEYS][HD]
+  __shared__ float q_s[SIG_DECODE_HEADS][HD];
+  __shared__ float w_s[SIG_DECODE_HEADS][SIG_DECODE_KEYS];
+  __shared__ float part_s[PARTS][SIG_DECODE_HEADS][HD];
+  const int b = seq_req[blockIdx.x];
+  if (b < 0) return;
+  const int tok = seq_tok[blockIdx.x];
+  const int g = blockIdx.y;
+  const int tid = threadIdx.x;
+  const int p = pos[tok];
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int part = tid / HD, d = tid - part * HD;
+  for (int h0 = 0; h0 < group; h0 += SIG_DECODE_HEADS) {
+    const int nh = min(SIG_DECODE_HEADS, group - h0);
+    for (int i = tid; i < nh * HD; i += SIG_DECODE_KEYS) {
+      const int h = i / HD, dd = i - h * HD;
+      q_s[h][dd] = __bfloat162float(q[(size_t)tok * q_stride + (g * group + h0 + h) * HD + dd]);
+    }
+    float acc[SIG_DECODE_HEADS];
+#pragma unroll
+    for (int h = 0; h < SIG_DECODE_HEADS; ++h) acc[h] = 0.f;
+    __syncthreads();
+    for (int k0 = lo / SIG_DECODE_KEYS * SIG_DECODE_KEYS; k0 <= p; k0 += SIG_DECODE_KEYS) {
+      const int j = k0 + tid;
+      long long base = -1;
+      if (j >= lo && j <= p) {
+        const int logical = j / page_size;
+        const int page = logical < table_width ? block_table[(size_t)b * table_width + logical] : -1;
+        if (page >= 0 && page < n_pages)
+          base = (((long long)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
+        else if (status)
+          atomicOr(status, FG_STATUS_BAD_PAGE);
+      }
+      float s[SIG_DECODE_HEADS];
+#pragma unroll
+      for (int h = 0; h < SIG_DECODE_HEADS; ++h) s[h] = 0.f;
+      uint4* v_row = reinterpret_cast<uint4*>(&v_s[tid][0]);
+      if (base >= 0) {
+        const uint4* k_row = reinterpret_cast<const uint4*>(k_pages + base);
+        const uint4* v_src = reinterpret_cast<const uint4*>(v_pages + base);
+#pragma unroll
+        for (int c = 0; c < HD / 8; ++c) v_row[c] = v_src[c];
+#pragma unroll
+        for (int c = 0; c < HD / 8; ++c) {
+          const uint4 raw = k_row[c];
+          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 kv = __bfloat1622float2(k2[e]);
+#pragma unroll
+            for (int h = 0; h < SIG_DECODE_HEADS; ++h) {
+              if (h < nh) {
+                s[h] = fmaf(q_s[h][c * 8 + 2 * e], kv.x, s[h]);
+                s[h] = fmaf(q_s[h][c * 8 + 2 * e + 1], kv.y, s[h]);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < HD / 8; ++c) v_row[c] = make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int h = 0; h < SIG_DECODE_HEADS; ++h) {
+        if (h < nh) {
+          float wgt = 0.f;
+          if (base >= 0) {
+            const int head = g * group + h0 + h;
+            float z = s[h] * scale + (gate != nullptr ? gate[head] : 0.f);
+            if (r1 != nullptr) z -= r1[head] * logf(1.f + r2[head] * (float)(p - j));
+            wgt = 1.f / (1.f + expf(-z));
+          }
+          w_s[h][tid] = wgt;
+        }
+      }
+      __syncthreads();
+      if (part < PARTS) {
+        const int j_end = min(SIG_DECODE_KEYS, (part + 1) * PART_KEYS);
+#pragma unroll 4
+        for (int jj = part * PART_KEYS; jj < j_end; ++jj) {
+          const float vv = __bfloat162float(v_s[jj][d]);
+#pragma unroll
+          for (int h = 0; h < SIG_DECODE_HEADS; ++h)
+            if (h < nh) acc[h] = fmaf(w_s[h][jj], vv, acc[h]);
+        }
+      }
+      __syncthreads();
+    }
+    if (part < PARTS) {
+#pragma unroll
+      for (int h = 0; h < SIG_DECODE_HEADS; ++h)
+        if (h < nh) part_s[part][h][d] = acc[h];
+    }
+    __syncthreads();
+    for (int i = tid; i < nh * HD; i += SIG_DECODE_KEYS) {
+      const int h = i / HD, dd = i - h * HD;
+      float total = 0.f;
+#pragma unroll
+      for (int pt = 0; pt < PARTS; ++pt) total += part_s[pt][h][dd];
+      out[(size_t)tok * out_stride + (g * group + h0 + h) * HD + dd] = __float2bfloat16_rn(total);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace fg_attn

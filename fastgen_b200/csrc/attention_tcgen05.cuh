@@ -49,6 +49,16 @@ constexpr int MAX_PARTS = 16;             // most parts of an item (one block ad
 // 2^x as the special-function unit gives it (relative error about 2^-22, results below
 // 2^-126 flushed to zero): the probabilities are rounded to bfloat16 right after, and
 // exp2f()'s extra range handling would cost three more instructions an element.
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -174,7 +184,13 @@ __device__ __noinline__ void merge_parts(const float* slots, int n_parts, __nv_b
 // SPLIT: the instantiation for launches that work on long items in parts (`parts` > 1); the
 // other one has none of that code (its main loop proved sensitive to it: head size 64 ran 5 %
 // slower with it).
-template <int HD, bool SPLIT>
+//
+// SIGMOID: the weight of a visible key is sigmoid(q.k * scale + gate_h - r1_h ln(1 + r2_h (i - j)))
+// (gate, r1, r2: float32 per query head; r1 and r2 may be null together) and nothing is normalised
+// over the keys: the softmax warps compute the weights in base 2 on the special-function unit
+// (lg2, ex2, rcp), keep no maximum and no sum, never rescale O and store it as it is.  Such a
+// launch does not split its items.
+template <int HD, bool SPLIT, bool SIGMOID = false>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              int layer, const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -184,8 +200,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              const int* __restrict__ tile_ntok, int n_tiles_total, int n_kv_heads, int group,
                              int heads_per_block, int window, float scale_log2, unsigned int* work_counter,
                              int parts, float* split_scratch, int* split_flags, int split_slots,
-                             const int* real_tiles, int* status) {
+                             const int* real_tiles, int* status, const float* __restrict__ gate,
+                             const float* __restrict__ dist_r1, const float* __restrict__ dist_r2) {
   static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
+  static_assert(!(SPLIT && SIGMOID), "launches with sigmoid weights do not split their items");
   constexpr int HALVES = HD / 64;
   constexpr int STAGE_BYTES = HALVES * KV_HALF;
   constexpr uint32_t IDESC_S = instr_desc(KEYS, false);
@@ -472,6 +490,16 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const uint32_t my_lane = (uint32_t)(warp * 32) << 16;  // this warp's quarter of the TMEM lanes
         float m_ref = -INFINITY, l_run = 0.f;
         const float c = scale_log2;
+        // sigmoid weights, in base 2: the row's gate and distance numbers
+        float gate_l2 = 0.f, r1_row = 0.f, r2_row = 0.f;
+        if (SIGMOID && my_valid) {
+          const int head = g * group + row_head(tid);
+          if (gate != nullptr) gate_l2 = gate[head] * 1.4426950408889634f;
+          if (dist_r1 != nullptr) {
+            r1_row = dist_r1[head];
+            r2_row = dist_r2[head];
+          }
+        }
         const bool warp_full = __all_sync(0xffffffffu, my_valid);
         int warp_max = my_pos, warp_min = my_valid ? my_pos : 0x7fffffff;
 #pragma unroll
@@ -489,6 +517,22 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           tmem_ld64(s_addr, s);
           const bool need_mask =
               !warp_full || k0 + KEYS - 1 > warp_min || (window > 0 && k0 <= warp_max - window);
+          float alpha = 1.f;
+          bool raise = false;
+          float sum = 0.f;
+          uint32_t packed[KEYS / 2];
+          if (SIGMOID) {
+            // 2^zl = e^z for z = score * scale + gate - r1 ln(1 + r2 distance); the weight is 1 / (1 + 2^-zl)
+            auto weight = [&](float sv, int j) {
+              float zl = fmaf(sv, c, gate_l2);
+              if (dist_r1 != nullptr) zl -= r1_row * lg2_approx(fmaf(r2_row, (float)(my_pos - j), 1.f));
+              const float wgt = rcp_approx(1.f + ex2_approx(-zl));
+              const bool vis = !need_mask || (my_pos >= 0 && j <= my_pos && (window <= 0 || j > my_pos - window));
+              return vis ? wgt : 0.f;
+            };
+#pragma unroll
+            for (int i = 0; i < KEYS; i += 2) packed[i / 2] = pack_bf16(weight(s[i], k0 + i), weight(s[i + 1], k0 + i + 1));
+          } else {
           if (need_mask) {
 #pragma unroll
             for (int i = 0; i < KEYS; ++i) {
@@ -509,15 +553,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           }
           const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
           // raise the reference maximum only when it pays (or when there is none yet)
-          float alpha = 1.f;
-          bool raise = false;
           if (mx != -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * c > RESCALE_THRESHOLD)) {
             raise = true;
             alpha = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mx) * c);
             m_ref = mx;
           }
-          float sum = 0.f;
-          uint32_t packed[KEYS / 2];
           if (m_ref == -INFINITY) {
 #pragma unroll
             for (int i = 0; i < KEYS / 2; ++i) packed[i] = 0u;
@@ -541,6 +581,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
             f32x2_split(sum2[1], a2, a3);
             sum = (a0 + a1) + (a2 + a3);
           }
+          }  // softmax
           l_run = l_run * alpha + sum;
           // P_t over the first 32 columns of S_t (this thread has read all of its row)
           tmem_st32_raw(s_addr, packed);
@@ -548,7 +589,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           // run (warp-uniform decision), once O_{t-1} is complete; otherwise the warp does not
           // wait for O at all.  (The barrier of this parity completes next for O_{t+1}, which
           // needs this thread's P_{t+1}: a wait on it cannot fall behind.)
-          if (t > 0 && __any_sync(0xffffffffu, raise)) {
+          if (!SIGMOID && t > 0 && __any_sync(0xffffffffu, raise)) {
             mbar_wait(&o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1, status, &gave_up);
             tc_fence_after();
 #pragma unroll
@@ -570,7 +611,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         __nv_bfloat16* dst =
             out + (size_t)(tok0 + row_token(tid)) * out_stride + (g * group + row_head(tid)) * HD;
         if (!split) {
-          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          const float inv = SIGMOID ? 1.f : (l_run > 0.f ? 1.f / l_run : 0.f);
 #pragma unroll
           for (int cc = 0; cc < HD / 32; ++cc) {
             float part_o[32];

@@ -64,6 +64,10 @@ _ATTN_SIGNATURES = {
     "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_attention_sigmoid": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                              _P, _P, _P, _P, _P],
+    "fg_attention_sigmoid_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I,
+                                              _I, _I, _F, _P, _P, _P, _P, _P, _P, _P],
+    "fg_attention_sigmoid_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F,
+                                         _P, _P, _P, _P, _P],
     "fg_attention_sigmoid_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                           _F, _P, _P, _P, _P, _P],
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
@@ -584,8 +588,9 @@ class Ops:
         ``sum_j sigmoid(q.k_j * scale + gate[h] - r1[h] * ln(1 + r2[h] * distance)) v_j`` over the
         visible keys; ``gate``, ``r1``, ``r2`` are float32 [heads] or ``None``.  float32: one
         CUDA-core kernel for all tokens.  bfloat16: prompt portions on the tensor cores
-        (``mma.sync``, the weights rounded to bfloat16 for the second product), single tokens on
-        the CUDA-core kernel, which reads a window's keys once."""
+        (``tcgen05.mma`` at head sizes 64 and 128 on pages the TMA can tile, else ``mma.sync``;
+        the weights rounded to bfloat16 for the second product), single tokens in a
+        kernel of their own, a block per (token, key/value head), which reads a window's keys once."""
         lib = attn(head_dim)
         k_pages, v_pages, block_table = memory.k_pages, memory.v_pages, memory.block_table
         assert q.stride(1) == 1 and out.stride(1) == 1
@@ -601,17 +606,27 @@ class Ops:
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), FG_F32, *head,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, *tail))
             return
-        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, PREFILL_ROWS), 2)
-        if tiles.n:
+        tc5 = memory.tensor_maps is not None and head_dim in (64, 128) and self.use_tcgen05
+        rows = PREFILL_TMA_ROWS if tc5 else PREFILL_ROWS
+        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, rows), 2)
+        if tiles.n and tc5:
+            # head sizes 64 and 128 on pages the TMA can tile: tcgen05.mma with the scores and the
+            # output in tensor memory, the weights computed by the kernel's softmax warps
+            _check(lib, lib.fg_attention_sigmoid_prefill_tc5_bf16(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[2].ptr, memory.tensor_maps[3].ptr,
+                memory.layer_index, _ptr(block_table), block_table.shape[1], memory.page_size, k_pages.shape[0],
+                _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads,
+                head_dim, int(window or 0), float(scale), _ptr(gate), _ptr(r1), _ptr(r2), _ptr(self._work_counter),
+                _ptr(tiles.count), _ptr(self.status), _stream()))
+        elif tiles.n:
             _check(lib, lib.fg_attention_sigmoid_prefill_bf16(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *head,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, *tail))
         singles = ctx.single_tokens()
         if singles.n:
-            # a list of single tokens: no token counts
-            _check(lib, lib.fg_attention_sigmoid(
-                _ptr(q), q.stride(0), _ptr(out), out.stride(0), FG_BF16, *head,
-                _ptr(singles.req), _ptr(singles.tok), None, singles.n, *tail))
+            _check(lib, lib.fg_attention_sigmoid_decode_bf16(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), *head,
+                _ptr(singles.req), _ptr(singles.tok), singles.n, *tail))
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,
                out_tokens, out_logprobs=None, scratch=None, with_status: bool = False) -> torch.Tensor:
