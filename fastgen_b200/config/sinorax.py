@@ -121,7 +121,7 @@ _MIXERS = {"attention": _softmax_attention, "attention_2": _sigmoid_attention}
 
 
 def sinorax_model_args(config: Mapping[str, Any]) -> ModelArgs:
-    require(config, ("vocab", "width", "layers", "logit_scale"), "Sinorax config.json")
+    require(config, ("vocab", "width", "layers"), "Sinorax config.json")
     dim = positive_int(config, "width")
     vocab = positive_int(config, "vocab")
     if not isinstance(config["layers"], (list, tuple)) or not config["layers"]:
@@ -192,7 +192,7 @@ def sinorax_model_args(config: Mapping[str, Any]) -> ModelArgs:
         schedule=tuple(ScheduleEntry(i) for i in range(len(layers))),
         final_norm=_norm(dim, "final.norm"),
         embedder=embedder,
-        logit_scale=float(config["logit_scale"]),
+        logit_scale=float(config.get("logit_scale", 1.0)),
         logit_softcap=float(cap) if cap else None,
         optional_tensors=tuple(optional),
     )

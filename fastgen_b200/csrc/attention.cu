@@ -110,22 +110,33 @@ extern "C" int fg_attention_sigmoid(const void* q, int q_stride, void* out, int 
 
 // Single tokens of the sigmoid-weighted attention in bfloat16: token seq_tok[i] of request
 // seq_req[i] (negative: padding, skipped).
+extern "C" int fg_attention_sigmoid_decode_keys() { return fg_attn::SIG_DECODE_KEYS; }
+
+// max_stretches bounds the stretches of fg_attention_sigmoid_decode_keys() positions that a token's
+// visible keys reach into; with more than one, `scratch` takes n_seqs * n_heads * max_stretches *
+// head size floats and a second kernel adds them up.
 extern "C" int fg_attention_sigmoid_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
                                                 const void* k_pages, const void* v_pages, const int* block_table,
                                                 int table_width, int page_size, int n_pages, const int* pos,
                                                 const int* seq_req, const int* seq_tok, int n_seqs, int n_heads,
                                                 int n_kv_heads, int head_dim, int window, float scale,
-                                                const float* gate, const float* r1, const float* r2, int* status,
+                                                const float* gate, const float* r1, const float* r2, float* scratch,
+                                                long long scratch_floats, int max_stretches, int* status,
                                                 cudaStream_t stream) {
   using namespace fg_attn;
   if (n_seqs == 0) return 0;
+  FG_CHECK_ARG(max_stretches >= 1 && max_stretches <= 65535, "fg_attention_sigmoid_decode_bf16: %d stretches",
+               max_stretches);
+  FG_CHECK_ARG(max_stretches == 1 || (scratch != nullptr && scratch_floats >= (long long)n_seqs * n_heads *
+                                                                                 max_stretches * FG_HEAD_DIM),
+               "fg_attention_sigmoid_decode_bf16: scratch of %lld floats is too small", scratch_floats);
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_sigmoid_decode_bf16: library built for head size %d, got %d",
                FG_HEAD_DIM, head_dim);
   FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
                "fg_attention_sigmoid_decode_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
   FG_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "fg_attention_sigmoid_decode_bf16: r1 and r2 come together");
   FG_CHECK_ARG(((uintptr_t)k_pages & 15) == 0, "fg_attention_sigmoid_decode_bf16: the key pool must be 16-byte aligned");
-  dim3 grid(n_seqs, n_kv_heads);
+  dim3 grid(n_seqs, n_kv_heads, max_stretches);
   constexpr size_t smem = sigmoid_decode_smem_bytes<FG_HEAD_DIM>();
   auto kern = attention_sigmoid_decode_kernel<FG_HEAD_DIM>;
   static bool attr_set = false;
@@ -137,8 +148,13 @@ extern "C" int fg_attention_sigmoid_decode_bf16(const void* q, int q_stride, voi
   kern<<<grid, SIG_DECODE_KEYS, smem, stream>>>(
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_kv_heads,
-      n_heads / n_kv_heads, window, scale, gate, r1, r2, status);
+      n_heads / n_kv_heads, window, scale, gate, r1, r2, scratch, status);
   FG_CHECK_LAUNCH("fg_attention_sigmoid_decode_bf16");
+  if (max_stretches > 1) {
+    attention_sigmoid_combine_kernel<FG_HEAD_DIM><<<dim3(n_seqs, n_heads), FG_HEAD_DIM < 128 ? 64 : 128, 0, stream>>>(
+        (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_stretches, scratch, status);
+    FG_CHECK_LAUNCH("fg_attention_sigmoid_decode_bf16 (combine)");
+  }
   return 0;
 }
 

@@ -172,16 +172,21 @@ attention_sigmoid_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------
-// Single tokens, bfloat16: one block per (token, key/value head) walks the token's visible keys
-// in stretches of SIG_DECODE_KEYS positions that start at multiples of that number.  A thread
+// Single tokens, bfloat16: the token's visible keys are cut into stretches of SIG_DECODE_KEYS
+// positions that start at multiples of that number, and a block takes one stretch for one
+// (token, key/value head): blockIdx.z counts the stretches from the first one the token sees,
+// blocks beyond its last one leave at once.  A thread
 // takes one key of the stretch: it reads the key's row and the value's row with 16-byte loads
 // (all of a stretch's loads are in flight together: one round trip to memory a stretch), leaves
 // the value in shared memory, forms the scores of the group's heads (float32, dimensions in
 // ascending order) and leaves the weights in shared memory; then the threads turn to the
 // output: thread (part, d) adds up weight * value over its part of the stretch's keys for
 // dimension d, the parts are added in ascending order at the end.  Nothing is normalised, so
-// there are no partial maxima and no merge: a token's result depends on its own position and
-// window only.  Groups of more than SIG_DECODE_HEADS heads take passes.
+// a stretch's partial output is a plain sum: it goes to scratch [token, head, stretch, HD]
+// (float32) and attention_sigmoid_combine_kernel adds a token's stretches in ascending order
+// (with one stretch a launch, gridDim.z == 1, the block writes the output itself).  A token's
+// result depends on its own position and window only.  Groups of more than SIG_DECODE_HEADS
+// heads take passes.
 // ---------------------------------------------------------------------------------
 constexpr int SIG_DECODE_KEYS = 256;   // = threads
 constexpr int SIG_DECODE_HEADS = 8;
@@ -199,7 +204,8 @@ attention_sigmoid_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
                                 int table_width, int page_size, int n_pages, const int* __restrict__ pos,
                                 const int* __restrict__ seq_req, const int* __restrict__ seq_tok, int n_kv_heads,
                                 int group, int window, float scale, const float* __restrict__ gate,
-                                const float* __restrict__ r1, const float* __restrict__ r2, int* status) {
+                                const float* __restrict__ r1, const float* __restrict__ r2, float* __restrict__ scratch,
+                                int* status) {
   constexpr int PARTS = SIG_DECODE_KEYS / HD;                    // threads side by side on one dimension
   constexpr int PART_KEYS = (SIG_DECODE_KEYS + PARTS - 1) / PARTS;
   extern __shared__ __align__(16) unsigned char sig_smem[];
@@ -215,6 +221,13 @@ attention_sigmoid_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
   const int p = pos[tok];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int part = tid / HD, d = tid - part * HD;
+  const int k0 = (lo / SIG_DECODE_KEYS + (int)blockIdx.z) * SIG_DECODE_KEYS;
+  if (k0 > p) return;
+  if (gridDim.z == 1 && k0 + SIG_DECODE_KEYS <= p) {
+    // the launch was sized for fewer stretches than this token has
+    if (tid == 0 && status) atomicOr(status, FG_STATUS_BAD_SPLITS);
+    return;
+  }
   for (int h0 = 0; h0 < group; h0 += SIG_DECODE_HEADS) {
     const int nh = min(SIG_DECODE_HEADS, group - h0);
     for (int i = tid; i < nh * HD; i += SIG_DECODE_KEYS) {
@@ -225,7 +238,7 @@ attention_sigmoid_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
 #pragma unroll
     for (int h = 0; h < SIG_DECODE_HEADS; ++h) acc[h] = 0.f;
     __syncthreads();
-    for (int k0 = lo / SIG_DECODE_KEYS * SIG_DECODE_KEYS; k0 <= p; k0 += SIG_DECODE_KEYS) {
+    {
       const int j = k0 + tid;
       long long base = -1;
       if (j >= lo && j <= p) {
@@ -302,9 +315,38 @@ attention_sigmoid_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
       float total = 0.f;
 #pragma unroll
       for (int pt = 0; pt < PARTS; ++pt) total += part_s[pt][h][dd];
-      out[(size_t)tok * out_stride + (g * group + h0 + h) * HD + dd] = __float2bfloat16_rn(total);
+      const int head = g * group + h0 + h;
+      if (gridDim.z == 1)
+        out[(size_t)tok * out_stride + head * HD + dd] = __float2bfloat16_rn(total);
+      else
+        scratch[(((size_t)blockIdx.x * (n_kv_heads * group) + head) * gridDim.z + blockIdx.z) * HD + dd] = total;
     }
     __syncthreads();
+  }
+}
+
+// out[token, head, :] = the sum of the token's stretches, in ascending order.  One block per
+// (token, head); the number of stretches follows from the token's position and the window.
+template <int HD>
+__global__ void attention_sigmoid_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride,
+                                                 const int* __restrict__ pos, const int* __restrict__ seq_req,
+                                                 const int* __restrict__ seq_tok, int n_heads, int window,
+                                                 int max_stretches, const float* scratch, int* status) {
+  if (seq_req[blockIdx.x] < 0) return;
+  const int tok = seq_tok[blockIdx.x];
+  const int head = blockIdx.y;
+  const int p = pos[tok];
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  int n = p / SIG_DECODE_KEYS - lo / SIG_DECODE_KEYS + 1;
+  if (n > max_stretches) {
+    if (threadIdx.x == 0 && status) atomicOr(status, FG_STATUS_BAD_SPLITS);
+    n = max_stretches;
+  }
+  const float* src = scratch + ((size_t)blockIdx.x * n_heads + head) * max_stretches * HD;
+  for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
+    float total = 0.f;
+    for (int z = 0; z < n; ++z) total += src[(size_t)z * HD + dd];
+    out[(size_t)tok * out_stride + head * HD + dd] = __float2bfloat16_rn(total);
   }
 }
 

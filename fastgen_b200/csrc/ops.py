@@ -67,7 +67,7 @@ _ATTN_SIGNATURES = {
     "fg_attention_sigmoid_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I,
                                               _I, _I, _F, _P, _P, _P, _P, _P, _P, _P],
     "fg_attention_sigmoid_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F,
-                                         _P, _P, _P, _P, _P],
+                                         _P, _P, _P, _P, ctypes.c_longlong, _I, _P, _P],
     "fg_attention_sigmoid_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                           _F, _P, _P, _P, _P, _P],
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
@@ -89,6 +89,7 @@ PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
 PREFILL_TMA_ROWS = 128  # ... of the bfloat16 prompt kernel with tiled TMA loads
 PREFILL_TMA_KEYS = 64   # key positions per tile of that kernel
 DECODE_SPLIT = 128   # key positions per split of the bfloat16 single-token kernel
+SIGMOID_DECODE_KEYS = 256  # key positions per stretch of the sigmoid attention's single-token kernel
 
 #: activations the products' epilogues and ``bias_act`` know
 ACTIVATIONS = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2}
@@ -162,6 +163,7 @@ def attn(head_dim: int):
         assert lib.fg_attention_rows_per_block() == SIMT_ROWS
         assert lib.fg_attention_prefill_rows() == PREFILL_ROWS
         assert lib.fg_attention_decode_split() == DECODE_SPLIT
+        assert lib.fg_attention_sigmoid_decode_keys() == SIGMOID_DECODE_KEYS
         _attn[head_dim] = lib
     return lib
 
@@ -624,9 +626,18 @@ class Ops:
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, *tail))
         singles = ctx.single_tokens()
         if singles.n:
+            # a token's keys reach into so many stretches at most: its window's, or all it can hold
+            keys = SIGMOID_DECODE_KEYS
+            stretches = -(-singles.max_len // keys)
+            if window:
+                stretches = min(stretches, -(-int(window) // keys) + 1)
+            stretches = max(1, stretches)
+            scratch = self._decode_scratch(singles.n * n_heads * stretches * head_dim) if stretches > 1 else None
             _check(lib, lib.fg_attention_sigmoid_decode_bf16(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *head,
-                _ptr(singles.req), _ptr(singles.tok), singles.n, *tail))
+                _ptr(singles.req), _ptr(singles.tok), singles.n, *tail[:-2], _ptr(scratch),
+                scratch.numel() if scratch is not None else 0, stretches, *tail[-2:]))
+            Ops.launches += int(stretches > 1)  # the sum of the stretches
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,
                out_tokens, out_logprobs=None, scratch=None, with_status: bool = False) -> torch.Tensor:

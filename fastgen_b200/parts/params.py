@@ -91,12 +91,15 @@ class AttentionParams:
                 f"{self.n_heads} query heads cannot be grouped over "
                 f"{self.n_kv_heads} key/value heads"
             )
-        for size in (self.head_dim, self.v_head_dim or self.head_dim):
-            if size % 2 != 0 or not 2 <= size <= 256:
+        for size, position in ((self.head_dim, self.position), (self.v_head_dim or self.head_dim, self.value_position)):
+            if not 1 <= size <= 256:
                 raise ValueError(
-                    f"head size {size} is not supported: the attention kernels take even "
-                    "sizes up to 256 (padded to a multiple of 16)"
+                    f"head size {size} is not supported: the attention kernels take sizes up to 256 "
+                    "(padded to a multiple of 16)"
                 )
+            turns = position is not None and getattr(position, "kind", "none") != "none"
+            if turns and size % 2 != 0 and getattr(position.params, "rot_dims", None) is None:
+                raise ValueError(f"head size {size} is odd: a rotation needs pairs of dimensions")
         if self.window is not None and self.window <= 0:
             raise ValueError(f"attention window must be positive, got {self.window}")
 

@@ -122,8 +122,9 @@ def test_description_reads_every_size_from_the_configuration():
 
 
 def test_description_errors_name_the_place():
-    with pytest.raises(ConfigError, match="logit_scale"):
-        model_args_from_config({k: v for k, v in SX_A.items() if k != "logit_scale"})
+    with pytest.raises(ConfigError, match="width"):
+        model_args_from_config({k: v for k, v in SX_A.items() if k != "width"})
+    assert model_args_from_config({k: v for k, v in SX_A.items() if k != "logit_scale"}).logit_scale == 1.0
     bad = json.loads(json.dumps(SX_A))
     bad["layers"][1]["type"] = "attention_9"
     with pytest.raises(ConfigError, match=r"layers\[1\].*attention_9"):
