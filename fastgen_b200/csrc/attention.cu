@@ -271,8 +271,8 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         int table_width, int page_size, int n_pages, const int* pos,
                                         const int* seq_req, const int* seq_tok, int n_seqs, int n_heads,
                                         int n_kv_heads, int head_dim, int window, float scale, float* scratch,
-                                        long long scratch_floats, int max_splits, int* status,
-                                        cudaStream_t stream) {
+                                        long long scratch_floats, int max_splits, const float* out_freqs,
+                                        int* status, cudaStream_t stream) {
   using namespace fg_mma;
   if (n_seqs == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_bf16: library built for head size %d, got %d",
@@ -305,7 +305,8 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
   FG_CHECK_LAUNCH("fg_attention_decode_bf16");
   dim3 cgrid(n_heads, n_seqs);
   attention_combine_kernel<FG_HEAD_DIM><<<cgrid, COMBINE_THREADS, 0, stream>>>(
-      scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, nullptr, status);
+      scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, nullptr, status,
+      out_freqs);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }
@@ -327,7 +328,7 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
                                             const int* seq_tok, int n_seqs, int n_heads, int n_kv_heads,
                                             int head_dim, int window, float scale, float* scratch,
                                             long long scratch_floats, int max_splits, long long max_pairs,
-                                            int* status, cudaStream_t stream) {
+                                            const float* out_freqs, int* status, cudaStream_t stream) {
   using namespace fg_tma;
   if (n_seqs == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_tma_bf16: library built for head size %d, got %d",
@@ -388,7 +389,7 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
   dim3 cgrid(n_heads, n_seqs);
   fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(fg_mma::COMBINE_THREADS), 0, stream,
                 (const float*)partials, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window,
-                max_splits, combine_pairs, status);
+                max_splits, combine_pairs, status, out_freqs);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }

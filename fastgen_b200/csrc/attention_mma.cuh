@@ -594,7 +594,10 @@ __global__ void __launch_bounds__(COMBINE_THREADS)
 attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, int out_stride,
                          const int* __restrict__ pos, const int* __restrict__ seq_req,
                          const int* __restrict__ seq_tok, int n_heads, int window, int max_splits,
-                         const int* first_pair, int* status) {
+                         const int* first_pair, int* status, const float* __restrict__ out_freqs) {
+  // out_freqs: null, or HD/2 frequencies by which the output's adjacent pairs are turned
+  // (angle position * frequency) before they are stored: a model that caches values turned by
+  // their positions turns the sum back here, with the negated table.
   // first_pair (written by the kernel before, so no __restrict__): null, or for every
   // request the number of (request, split) pairs before it; the partials are then
   // numbered [pair][head] (only the splits that exist), else [request][head][split].
@@ -671,6 +674,22 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
 #pragma unroll
   for (int w = 0; w < WARPS; ++w) total += ll_s[w];
   const float inv = total > 0.f ? 1.f / total : 0.f;
+  if (out_freqs != nullptr) {
+    for (int j = tid; j < HD / 2; j += COMBINE_THREADS) {
+      float re = 0.f, im = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        re += acc_s[w][2 * j];
+        im += acc_s[w][2 * j + 1];
+      }
+      re *= inv;
+      im *= inv;
+      float sn, cs;
+      sincosf((float)p * out_freqs[j], &sn, &cs);
+      *reinterpret_cast<__nv_bfloat162*>(dst + 2 * j) = __floats2bfloat162_rn(re * cs - im * sn, im * cs + re * sn);
+    }
+    return;
+  }
   for (int d = tid; d < HD; d += COMBINE_THREADS) {
     float a = 0.f;
 #pragma unroll

@@ -72,14 +72,14 @@ _ATTN_SIGNATURES = {
                                           _F, _P, _P, _P, _P, _P],
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
-                                 ctypes.c_longlong, _I, _P, _P],
+                                 ctypes.c_longlong, _I, _P, _P, _P],
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P, _P, _I, _I, _P, _I, _P, _P],
     "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I, _I],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
-                                     _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P],
+                                     _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P, _P],
     "fg_attention_decode_is_persistent": [_I, _I, _I, _I],
 }
 
@@ -506,12 +506,17 @@ class Ops:
         return scratch, flags, room
 
     def attention(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
-                  window: Optional[int], scale: float) -> None:
+                  window: Optional[int], scale: float, out_freqs: Optional[torch.Tensor] = None) -> bool:
         """Paged causal attention of the step's query tokens; ``memory`` is the
         run's :class:`~fastgen_b200.cache.LayerMemory`, ``ctx`` the step's
         context.  bfloat16 runs on the tensor cores: prompt portions in one
         kernel, single tokens in a split-and-combine pair (with tiled TMA loads
-        where the shapes allow); float32 runs one CUDA-core kernel for all."""
+        where the shapes allow); float32 runs one CUDA-core kernel for all.
+
+        ``out_freqs`` (a frequency table, or ``None``): the caller wants the outputs' adjacent
+        pairs turned by ``position * frequency``.  Returns ``True`` if the kernels did that for
+        every token of the step (a bfloat16 step of single tokens only: the merge of the splits
+        turns what it stores), ``False`` if the caller still has to (``rotate_heads``)."""
         lib = attn(head_dim)
         k_pages, v_pages, block_table, page_size = (
             memory.k_pages, memory.v_pages, memory.block_table, memory.page_size)
@@ -525,7 +530,7 @@ class Ops:
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
                 n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
                 _ptr(self.status), _stream()))
-            return
+            return False
         use_tma = memory.tensor_maps is not None
         rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
         tiling = attention_tiling(n_heads, n_kv_heads, rows)
@@ -555,6 +560,8 @@ class Ops:
                 n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
                 _ptr(self.status), _stream()))
         singles = ctx.single_tokens()
+        fused = out_freqs is not None and tiles.n == 0 and singles.n > 0
+        turn = _ptr(out_freqs) if fused else None
         if singles.n:
             max_splits = max(1, -(-singles.max_len // DECODE_SPLIT))
             tma = use_tma and n_heads // n_kv_heads <= 16
@@ -571,12 +578,14 @@ class Ops:
                 _check(lib, lib.fg_attention_decode_tma_bf16(
                     _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,
                     memory.tensor_maps[1].ptr, memory.layer_index, _ptr(block_table),
-                    block_table.shape[1], page_size, k_pages.shape[0], _ptr(ctx.pos), *head, pairs,
+                    block_table.shape[1], page_size, k_pages.shape[0], _ptr(ctx.pos), *head, pairs, turn,
                     _ptr(self.status), _stream()))
             else:
                 _check(lib, lib.fg_attention_decode_bf16(
-                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *head, _ptr(self.status), _stream()))
+                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *head, turn, _ptr(self.status),
+                    _stream()))
             Ops.launches += 1  # the combine kernel
+        return fused
 
     def rotate_heads(self, x, pos, req, freqs, n_heads: int, head_dim: int) -> torch.Tensor:
         """Rotate the adjacent pairs of every head of ``x`` [T, heads*head_dim] in place by

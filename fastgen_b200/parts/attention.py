@@ -145,9 +145,12 @@ class GQAAttention(Mixer):
             table = torch.cat([table, table.new_zeros(self.hd // 2 - table.numel())]).contiguous()
         return table
 
-    def _attend(self, q, o, ctx, memory) -> None:
+    def _attend(self, q, o, ctx, memory) -> bool:
+        """Attention of the step's tokens into ``o``.  Returns whether the outputs have been turned
+        back already (values cached turned by their positions): the kernels do it where they can."""
         p = self.params
-        self.ops.attention(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale)
+        return self.ops.attention(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale,
+                                  out_freqs=self.v_unfreqs)
 
     def forward(self, x, ctx, memory):
         p, ops = self.params, self.ops
@@ -173,8 +176,8 @@ class GQAAttention(Mixer):
                 memory.block_table, memory.page_size, p.n_heads, p.n_kv_heads, self.hd, v_freqs=self.v_freqs,
             )
         o = torch.empty((t, self.q_width), dtype=x.dtype, device=x.device)
-        self._attend(q, o, ctx, memory)
-        if self.v_unfreqs is not None:
+        turned = self._attend(q, o, ctx, memory)
+        if self.v_unfreqs is not None and not turned:
             # the sum over values that were turned by their own positions is turned back by the query's
             ops.rotate_heads(o, ctx.pos, ctx.req, self.v_unfreqs, p.n_heads, self.hd)
         return ops.linear(o, self.wo, bias=self.bo)
@@ -207,10 +210,11 @@ class SigmoidAttention(GQAAttention):
         self.r2 = tensors["r2"].float().contiguous() if p.distance_bias else None
         self.gate = tensors["gate"].float().contiguous() if p.gate else None
 
-    def _attend(self, q, o, ctx, memory) -> None:
+    def _attend(self, q, o, ctx, memory) -> bool:
         p = self.params
         self.ops.attention_sigmoid(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale,
                                    gate=self.gate, r1=self.r1, r2=self.r2)
+        return False
 
 
 register_mixer("gqa_attention", GQAAttention)
