@@ -334,6 +334,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       const __nv_bfloat16* vs = Vs + (t & 1) * PREFILL_KEYS * LD;
       float s[NT][4];
       qk_product<HD, NT>(s, qf, ks, lane);
+      // distances as floats: a conversion a tile and row, a subtraction a key
+      const float dist0[2] = {(float)(p0 - k0 - 2 * (lane & 3)), (float)(p1 - k0 - 2 * (lane & 3))};
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -347,7 +349,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
               float z = s[nt][e] * scale_log2 + gate_r[e >> 1];
               // the special-function unit's logarithm, exponential and reciprocal: a few units in the
               // last place of float32, far below the bfloat16 rounding of the weight that follows
-              if (dist_r1 != nullptr) z -= r1_r[e >> 1] * __logf(1.f + r2_r[e >> 1] * (float)(p - j));
+              if (dist_r1 != nullptr) z -= r1_r[e >> 1] * __logf(1.f + r2_r[e >> 1] * (dist0[e >> 1] - (float)(nt * 8 + (e & 1))));
               wgt = __bfloat162float(__float2bfloat16_rn(__fdividef(1.f, 1.f + __expf(-z))));
             }
             s[nt][e] = wgt;

@@ -523,15 +523,19 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           uint32_t packed[KEYS / 2];
           if (SIGMOID) {
             // 2^zl = e^z for z = score * scale + gate - r1 ln(1 + r2 distance); the weight is 1 / (1 + 2^-zl)
-            auto weight = [&](float sv, int j) {
+            // (the distance as a float: one conversion a tile and a subtraction a key -- conversions
+            // run on the special-function unit, which is this kernel's busiest pipe)
+            const float dist0 = (float)(my_pos - k0);
+            auto weight = [&](float sv, int i) {
+              const int j = k0 + i;
               float zl = fmaf(sv, c, gate_l2);
-              if (dist_r1 != nullptr) zl -= r1_row * lg2_approx(fmaf(r2_row, (float)(my_pos - j), 1.f));
+              if (dist_r1 != nullptr) zl -= r1_row * lg2_approx(fmaf(r2_row, dist0 - (float)i, 1.f));
               const float wgt = rcp_approx(1.f + ex2_approx(-zl));
               const bool vis = !need_mask || (my_pos >= 0 && j <= my_pos && (window <= 0 || j > my_pos - window));
               return vis ? wgt : 0.f;
             };
 #pragma unroll
-            for (int i = 0; i < KEYS; i += 2) packed[i / 2] = pack_bf16(weight(s[i], k0 + i), weight(s[i + 1], k0 + i + 1));
+            for (int i = 0; i < KEYS; i += 2) packed[i / 2] = pack_bf16(weight(s[i], i), weight(s[i + 1], i + 1));
           } else {
           if (need_mask) {
 #pragma unroll

@@ -203,6 +203,33 @@ def test_dynamic_tanh_alone_and_fused_with_the_sum(dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_summand_with_a_norm_of_another_kind(dtype):
+    """The closing norm of a sub-layer need not be of the kind of the norm that follows: an
+    RMSNorm after a Dynamic Tanh summand, and the other way round, compose the same sum."""
+    import plain_llama as pl
+    from fastgen_b200.parts import RMSNormParams, make_norm
+
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(3)
+    tol = dict(rtol=1e-5, atol=5e-6) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    dyt, wd = _dyt_part(64, g, ops, "a")
+    rms = make_norm(PartSpec("rmsnorm", RMSNormParams(64, 1e-5), {"weight": "w"}))
+    w = (1 + 0.1 * torch.randn(64, generator=g)).bfloat16()
+    rms.bind({"weight": w.to(DEV)}, ops)
+    h = torch.randn(5, 64, generator=g).to(DEV)
+    d = torch.randn(5, 64, generator=g).to(DEV, dtype)
+    hd, dd = h.double().cpu(), d.double().cpu()
+    out = rms.add_forward(h.clone(), d, delta_norm=dyt)
+    assert torch.allclose(out.double().cpu(), pl.rmsnorm(hd + ps.dyt(dd, wd, "a"), w.double(), 1e-5), **tol)
+    out = dyt.add_forward(h.clone(), d, delta_norm=rms)
+    assert torch.allclose(out.double().cpu(), ps.dyt(hd + pl.rmsnorm(dd, w.double(), 1e-5), wd, "a"), **tol)
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    out = rms.add_forward(h.clone(), d, rows=rows, delta_norm=dyt)
+    assert torch.allclose(out.double().cpu(), pl.rmsnorm(hd + ps.dyt(dd, wd, "a"), w.double(), 1e-5)[[4, 1]], **tol)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens", [3, 40])
 def test_dense_feed_forward_alone(dtype, tokens):
     """A few tokens (the activation is the epilogue of the weight-streaming product) and many
@@ -382,13 +409,15 @@ def test_sigmoid_mixer_alone(dtype, sizes):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["prompt", "decoded"])
-def test_sigmoid_window_edge_shows(dtype, mode):
+@pytest.mark.parametrize("d", [16, 64, 128])
+def test_sigmoid_window_edge_shows(dtype, mode, d):
     """The key just outside the window would carry the whole output if it were seen, and the key
     just inside does: queries and keys are made so that the scores of these two keys stand out
     against hundreds of others, in a prompt portion and for a token decoded alone."""
-    heads, kv, d, dv, window, n = 2, 1, 16, 16, 70, 200
+    # (head sizes 64 and 128 take the tcgen05 prompt kernel in bfloat16, 16 the mma.sync one)
+    heads, kv, dv, window, n = 2, 1, d, 70, 200
     g = torch.Generator().manual_seed(11)
-    m = _attn(heads, kv, d, dv, 1.0, mask=window)
+    m = _attn(heads, kv, d, dv, 16.0 / d, mask=window)
 
     def tweak(w):
         w["mix.pb"] = torch.full((heads,), -12.0).bfloat16()  # an ordinary key weighs e^-12
