@@ -344,15 +344,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
           const int p = (e < 2) ? p0 : p1;
           const bool vis = p >= 0 && j <= p && (window <= 0 || j > p - window);
           if (SIGMOID) {
-            float wgt = 0.f;
-            if (vis) {
+            float wgt;
+            {
+              // (computed for every key and chosen afterwards: behind a branch the chain of special
+              // functions does not overlap between keys)
               float z = s[nt][e] * scale_log2 + gate_r[e >> 1];
               // the special-function unit's logarithm, exponential and reciprocal: a few units in the
               // last place of float32, far below the bfloat16 rounding of the weight that follows
               if (dist_r1 != nullptr) z -= r1_r[e >> 1] * __logf(1.f + r2_r[e >> 1] * (dist0[e >> 1] - (float)(nt * 8 + (e & 1))));
               wgt = __bfloat162float(__float2bfloat16_rn(__fdividef(1.f, 1.f + __expf(-z))));
             }
-            s[nt][e] = wgt;
+            s[nt][e] = vis ? wgt : 0.f;
           } else {
             s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
           }
