@@ -94,10 +94,25 @@ class CacheGroup:
     dirty: List[Tuple[int, int, int]] = field(default_factory=list)  # (slot, col, page)
 
     def first_needed_page(self, length: int) -> int:
-        """Lowest logical page that a query at position >= ``length`` may read."""
+        """Lowest logical page of the window of a query at position >= ``length``."""
         if self.spec.window is None:
             return 0
         return max(0, length - self.spec.window + 1) // self.page_size
+
+    @property
+    def kept_pages(self) -> int:
+        """Logical pages at a sequence's start that a window never releases: those that hold some of
+        the first positions every later query still sees."""
+        if self.spec.window is None or not self.spec.keep_first:
+            return 0
+        return -(-self.spec.keep_first // self.page_size)
+
+    def needed_pages(self, length: int, new_length: int):
+        """Logical pages a request that holds ``length`` tokens needs to hold ``new_length``."""
+        first = self.first_needed_page(length)
+        last = (new_length - 1) // self.page_size if new_length > 0 else -1
+        kept = min(self.kept_pages, first)
+        return [*range(0, min(kept, last + 1)), *range(first, last + 1)]
 
     def bytes_per_token(self, elt_size: int) -> int:
         return self.spec.n_pools * len(self.entries) * self.spec.n_kv_heads * self.spec.head_dim * elt_size
@@ -276,9 +291,7 @@ class CacheManager:
         out = []
         for gi, grp in enumerate(self.groups):
             have = req.pages[gi]
-            first = grp.first_needed_page(req.length)
-            last = (new_length - 1) // grp.page_size if new_length > 0 else -1
-            out.append(sum(1 for lp in range(first, last + 1) if lp not in have))
+            out.append(sum(1 for lp in grp.needed_pages(req.length, new_length) if lp not in have))
         return out
 
     def pages_for(self, length: int) -> List[int]:
@@ -325,9 +338,7 @@ class CacheManager:
                     f"free: {self.free_pages()}"
                 )
         for gi, grp in enumerate(self.groups):
-            first = grp.first_needed_page(req.length)
-            last = (new_length - 1) // grp.page_size if new_length > 0 else -1
-            missing = [lp for lp in range(first, last + 1) if lp not in req.pages[gi]]
+            missing = [lp for lp in grp.needed_pages(req.length, new_length) if lp not in req.pages[gi]]
             for lp, page in zip(missing, grp.pool.take(len(missing))):
                 req.pages[gi][lp] = page
                 grp.host_table[req.slot, lp] = page
@@ -344,7 +355,7 @@ class CacheManager:
         req.length = new_length
         for gi, grp in enumerate(self.groups):
             first = grp.first_needed_page(new_length)
-            gone = [lp for lp in req.pages[gi] if lp < first]
+            gone = [lp for lp in req.pages[gi] if grp.kept_pages <= lp < first]
             if gone:
                 grp.pool.give([req.pages[gi].pop(lp) for lp in gone])
                 for lp in gone:
@@ -427,10 +438,10 @@ class CacheManager:
                     seen[page] = req.request_id
                     if grp.host_table[req.slot, lp] != page:
                         raise CacheError("block table disagrees with a request's pages")
-                held = req.pages[gi]
+                held = [lp for lp in req.pages[gi] if lp >= grp.kept_pages] or list(req.pages[gi])
                 if held and sorted(held) != list(range(min(held), max(held) + 1)):
                     raise CacheError(f"request {req.request_id!r} holds a broken run of pages in group {gi}")
-                if req.reserved > ((max(held) + 1) * grp.page_size if held else 0):
+                if req.reserved > ((max(req.pages[gi]) + 1) * grp.page_size if req.pages[gi] else 0):
                     raise CacheError(f"request {req.request_id!r}: reserved bound beyond its pages in group {gi}")
             if len(seen) + grp.pool.n_free != grp.pool.n_pages:
                 raise CacheError(

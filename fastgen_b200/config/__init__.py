@@ -14,6 +14,7 @@ from .registry import (
 )
 from . import llama as _llama  # registers LlamaForCausalLM
 from . import sinorax as _sinorax  # registers Sinorax
+from . import zeladra as _zeladra  # registers Zeladra
 
 __all__ = [
     "ConfigError",

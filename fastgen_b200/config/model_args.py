@@ -91,6 +91,9 @@ class ModelArgs:
     logit_softcap: Optional[float] = None
     #: tensors a checkpoint may hold without the model using them
     optional_tensors: Sequence[str] = ()
+    #: so many residual streams side by side ([T, streams, dim], all equal to the embedding at the
+    #: start, summed before the final norm); ``None``: the one ordinary stream [T, dim]
+    streams: Optional[int] = None
 
     def __post_init__(self) -> None:
         n = len(self.layers)

@@ -23,7 +23,7 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
                                  int table_width, int page_size, int n_pages, const int* pos,
                                  const int* tile_req, const int* tile_tok0, const int* tile_ntok,
                                  int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
-                                 float scale, int* status, cudaStream_t stream) {
+                                 int keep_first, float scale, int* status, cudaStream_t stream) {
   using namespace fg_attn;
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_simt: library built for head size %d, got %d",
@@ -43,7 +43,7 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
     kern<<<grid, THREADS, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
                                           (const float*)k_pages, (const float*)v_pages, block_table,
                                           table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-                                          tile_ntok, n_kv_heads, group, hpb, window, scale, status);
+                                          tile_ntok, n_kv_heads, group, hpb, window, keep_first, scale, status);
   } else if (dtype == FG_BF16) {
     auto kern = attention_simt_kernel<__nv_bfloat16, FG_HEAD_DIM>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -51,8 +51,8 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
     kern<<<grid, THREADS, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_width,
-        page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_kv_heads, group, hpb, window, scale,
-        status);
+        page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_kv_heads, group, hpb, window, keep_first,
+        scale, status);
   } else {
     FG_CHECK_ARG(false, "fg_attention_simt: bad dtype %d", dtype);
   }

@@ -10,8 +10,8 @@
 // cut, what else is in the batch, or which pages hold the keys.
 //
 // Semantics of fastgen/forward.py:176-258: softmax(q.k * scale) v over the
-// positions j <= pos(query) of the query's own request (and j > pos - window
-// when a window is given), grouped-query heads h -> h / (Hq/Hkv).
+// positions j <= pos(query) of the query's own request (and, when a window is given,
+// j > pos - window or j < keep_first: the first positions stay visible), grouped-query heads h -> h / (Hq/Hkv).
 // Running maximum, sum and output accumulator are float32; exp is expf.
 //
 // Storage type T (float or bf16) only affects loads and the final store.
@@ -32,8 +32,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ block_table, int table_width, int page_size,
                       int n_pages, const int* __restrict__ pos, const int* __restrict__ tile_req,
                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
-                      int n_kv_heads, int group, int heads_per_block, int window, float scale,
-                      int* status) {
+                      int n_kv_heads, int group, int heads_per_block, int window, int keep_first,
+                      float scale, int* status) {
   constexpr int HP = HD + 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float(*Qs)[HP] = reinterpret_cast<float(*)[HP]>(smem_raw);
@@ -87,8 +87,13 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
     }
   }
   if (max_pos < 0) return;
-  int k_lo = 0;
-  if (window > 0) k_lo = max(0, min_pos - window + 1) / KEYS * KEYS;
+  // with a window, tiles that lie wholly before the earliest row's window are skipped, apart
+  // from those that hold some of the first `keep_first` positions, which stay visible for good
+  int k_win = 0, k_keep_end = 0;
+  if (window > 0) {
+    k_win = max(0, min_pos - window + 1) / KEYS * KEYS;
+    k_keep_end = min(k_win, (max(keep_first, 0) + KEYS - 1) / KEYS * KEYS);
+  }
 
   // this thread's 4 score rows: warp, warp+4, warp+8, warp+12; column = lane
   float m_run[4], l_run[4];
@@ -104,7 +109,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
   for (int i = 0; i < OD; ++i) o_acc[i] = 0.f;
   const int o_row = tid >> 3, o_col = tid & 7;
 
-  for (int k0 = k_lo; k0 <= max_pos; k0 += KEYS) {
+  for (int k0 = 0; k0 <= max_pos; k0 += KEYS) {
+    if (k0 >= k_keep_end && k0 < k_win) k0 = k_win;
     if (tid < KEYS) {
       const int j = k0 + tid;
       long long base = -1;
@@ -113,7 +119,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         const int page = logical < table_width ? block_table[(size_t)b * table_width + logical] : -1;
         if (page >= 0 && page < n_pages) {
           base = (((long long)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
-        } else if (window <= 0 || j > min_pos - window) {
+        } else if (window <= 0 || j > min_pos - window || j < keep_first) {
           // a key some row must see has no page
           if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
         }
@@ -147,7 +153,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
     for (int i = 0; i < 4; ++i) {
       const int r = warp + 4 * i;
       const int p = row_pos[r];
-      const bool visible = has_key && p >= 0 && j <= p && (window <= 0 || j > p - window);
+      const bool visible = has_key && p >= 0 && j <= p && (window <= 0 || j > p - window || j < keep_first);
       const float sv = visible ? s[i] * scale : -INFINITY;
       const float m_tile = warp_max(sv);
       const float m_new = fmaxf(m_run[i], m_tile);

@@ -40,6 +40,9 @@ CORE_SOURCES = [
     "embedding.cu",
     "rmsnorm.cu",
     "dyt.cu",
+    "stream_norm.cu",
+    "mamba2.cu",
+    "latent.cu",
     "activation.cu",
     "rope_kv.cu",
     "silu_gate.cu",

@@ -1,32 +1,39 @@
-// Token embedding: out[t, :] = table[token[t], :].
+// Token embedding: out[t, :] = table[token[t], :] * scale, written `copies` times side by
+// side (out is [T, copies, dim]: a model with several residual streams starts them equal).
 // Replaces F.embedding of fastgen/forward.py:403-410.  The output is the
-// residual stream, which the engine keeps in float32 in every mode.
+// residual stream, which the engine keeps in float32 in every mode; the product with the
+// scale is a float32 product.
 #include "common.cuh"
 
 template <typename TT, typename TO>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ tokens,
-                                 TO* __restrict__ out, int dim, int vocab, int* status) {
+                                 TO* __restrict__ out, int dim, int vocab, float scale, int copies,
+                                 int* status) {
   const int t = blockIdx.x;
   int tok = tokens[t];
+  TO* o = out + (size_t)t * copies * dim;
   if (tok < 0 || tok >= vocab) {
     if (threadIdx.x == 0 && status) atomicOr(status, FG_STATUS_BAD_TOKEN);
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) out[(size_t)t * dim + d] = from_f32<TO>(0.f);
+    for (int d = threadIdx.x; d < copies * dim; d += blockDim.x) o[d] = from_f32<TO>(0.f);
     return;
   }
   const TT* row = table + (size_t)tok * dim;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x)
-    out[(size_t)t * dim + d] = from_f32<TO>(to_f32<TT>(row[d]));
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const TO v = from_f32<TO>(to_f32<TT>(row[d]) * scale);
+    for (int c = 0; c < copies; ++c) o[(size_t)c * dim + d] = v;
+  }
 }
 
 extern "C" int fg_embedding(const void* table, int table_dtype, const int* tokens, void* out,
-                            int out_dtype, int n_tokens, int dim, int vocab, int* status,
-                            cudaStream_t stream) {
+                            int out_dtype, int n_tokens, int dim, int vocab, float scale, int copies,
+                            int* status, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  FG_CHECK_ARG(dim > 0 && vocab > 0, "fg_embedding: bad sizes dim=%d vocab=%d", dim, vocab);
+  FG_CHECK_ARG(dim > 0 && vocab > 0 && copies > 0, "fg_embedding: bad sizes dim=%d vocab=%d copies=%d", dim, vocab,
+               copies);
   const int threads = dim >= 1024 ? 256 : 128;
 #define LAUNCH(TT, TO)                                                        \
   embedding_kernel<TT, TO><<<n_tokens, threads, 0, stream>>>(                 \
-      (const TT*)table, tokens, (TO*)out, dim, vocab, status)
+      (const TT*)table, tokens, (TO*)out, dim, vocab, scale, copies, status)
   if (table_dtype == FG_F32 && out_dtype == FG_F32) LAUNCH(float, float);
   else if (table_dtype == FG_BF16 && out_dtype == FG_F32) LAUNCH(__nv_bfloat16, float);
   else if (table_dtype == FG_BF16 && out_dtype == FG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

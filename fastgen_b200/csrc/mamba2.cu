@@ -1,0 +1,310 @@
+// The state-space mixer (Mamba-2 form): short causal convolution with SiLU, the recurrence
+// over a per-head matrix state, and the gated norm of its output.
+//
+// The mixer's input projection gives, per token, a row [z | x | B | C | dt] (inner, inner,
+// groups*N, groups*N, heads columns).  x, B and C ("xBC", `channels` columns) pass the
+// convolution; then, per head h with group g = h / (heads / groups), in float32:
+//
+//   dt = softplus(dt_raw + dt_bias[h]);   a = exp(-exp(A_log[h]) * dt)
+//   S <- a * S + dt * B x^T      (S is N x P, P the head's value size)
+//   y = S^T C + D[h] * x
+//
+// A request's state lives in one float32 row per slot: [heads, N, P] for S, then
+// [taps-1, channels] for the convolution's last inputs (oldest first).  It is zero at
+// admission, which is also "zeros before the start" for the convolution.  A step may bring a
+// sequence any number of tokens; sequences are consecutive runs of tokens with one slot, and
+// tokens of slot < 0 are padding that touches nothing.
+//
+// The recurrence runs token by token, so its sums do not depend on how a prompt was cut or
+// what else is in the batch.
+#include "common.cuh"
+
+// ---- convolution + SiLU ---------------------------------------------------------------------
+// out[t, c] = silu(bias[c] + sum_k w[c, k] * in[t - (taps-1-k), c]); inputs before the step's
+// first token of the sequence come from the state.
+constexpr int CONV_THREADS = 128;
+constexpr int CONV_TOKENS = 8;
+constexpr int CONV_MAX_TAPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(CONV_THREADS)
+conv_silu_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ out, long out_stride,
+                 const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state,
+                 long state_stride, long conv_offset, const int* __restrict__ req, int n_tokens, int channels,
+                 int taps) {
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  if (c >= channels) return;
+  float wk[CONV_MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_TAPS; ++k) wk[k] = k < taps ? w[(size_t)c * taps + k] : 0.f;
+  const float bc = bias ? bias[c] : 0.f;
+  const int t0 = blockIdx.x * CONV_TOKENS;
+  for (int t = t0; t < min(t0 + CONV_TOKENS, n_tokens); ++t) {
+    const int slot = req[t];
+    if (slot < 0) continue;
+    // how many of the taps-1 tokens before t the step itself brings
+    int have = 0;
+    while (have < taps - 1 && t - have - 1 >= 0 && req[t - have - 1] == slot) ++have;
+    const float* st = state + (size_t)slot * state_stride + conv_offset;
+    float acc = bc;
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; ++k) {
+      if (k < taps) {
+        const int back = taps - 1 - k;  // this tap meets the input `back` tokens ago
+        float v;
+        if (back <= have) v = to_f32<T>(in[(size_t)(t - back) * in_stride + c]);
+        else v = st[(size_t)(taps - 1 + have - back) * channels + c];
+        acc = fmaf(wk[k], v, acc);
+      }
+    }
+    out[(size_t)t * out_stride + c] = acc / (1.f + expf(-acc));
+  }
+}
+
+// The state's convolution inputs after the step: the last taps-1 of (old inputs, new inputs).
+template <typename T>
+__global__ void __launch_bounds__(CONV_THREADS)
+conv_state_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ state, long state_stride,
+                  long conv_offset, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                  int channels, int taps) {
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  const int slot = seq_slot[blockIdx.x];
+  if (c >= channels || slot < 0) return;
+  const int start = seq_start[blockIdx.x], n = seq_start[blockIdx.x + 1] - start;
+  float* st = state + (size_t)slot * state_stride + conv_offset;
+  // ascending k: entry k + n is read before any write reaches it
+  for (int k = 0; k < taps - 1; ++k) {
+    const int j = n - (taps - 1) + k;
+    const float v = j >= 0 ? to_f32<T>(in[(size_t)(start + j) * in_stride + c]) : st[(size_t)(k + n) * channels + c];
+    st[(size_t)k * channels + c] = v;
+  }
+}
+
+// ---- the recurrence ---------------------------------------------------------------------------
+// A block works on (sequence, head, 16 columns of P); a thread on one column p and every
+// eighth row n of the state, which it keeps in registers.  Tokens are staged through shared
+// memory eight at a time.
+constexpr int SCAN_PB = 16;      // columns of P a block
+constexpr int SCAN_LANES = 8;    // threads a column
+constexpr int SCAN_THREADS = SCAN_PB * SCAN_LANES;
+constexpr int SCAN_TOKENS = 8;   // tokens a stage
+
+template <typename T, int NPT>
+__global__ void __launch_bounds__(SCAN_THREADS)
+ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restrict__ dt_raw, long dt_stride,
+                const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                float* __restrict__ y, long y_stride, float* __restrict__ state, long state_stride,
+                const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int heads, int groups,
+                int N, int P) {
+  extern __shared__ float smem[];
+  float* Bs = smem;                        // [SCAN_TOKENS][N]
+  float* Cs = Bs + SCAN_TOKENS * N;        // [SCAN_TOKENS][N]
+  float* xs = Cs + SCAN_TOKENS * N;        // [SCAN_TOKENS][SCAN_PB]
+  float* dts = xs + SCAN_TOKENS * SCAN_PB;  // [SCAN_TOKENS]
+  float* decs = dts + SCAN_TOKENS;         // [SCAN_TOKENS]
+
+  const int slot = seq_slot[blockIdx.x];
+  if (slot < 0) return;
+  const int start = seq_start[blockIdx.x], n_tok = seq_start[blockIdx.x + 1] - start;
+  const int h = blockIdx.y, g = h / (heads / groups);
+  const int p0 = blockIdx.z * SCAN_PB;
+  const int tid = threadIdx.x;
+  const int pl = tid / SCAN_LANES, lane = tid % SCAN_LANES;
+  const int p = p0 + pl;
+  const bool p_ok = p < P;
+  const int inner = heads * P;
+  const float bias = dt_bias[h];
+  const float a = -expf(a_log[h]);
+  const float dsk = d_skip[h];
+
+  float* S = state + (size_t)slot * state_stride + (size_t)h * N * P;
+  float s[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = lane + SCAN_LANES * i;
+    s[i] = (p_ok && n < N) ? S[(size_t)n * P + p] : 0.f;
+  }
+
+  for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
+    const int nt = min(SCAN_TOKENS, n_tok - t0);
+    __syncthreads();
+    for (int i = tid; i < nt * N; i += SCAN_THREADS) {
+      const int tt = i / N, n = i - tt * N;
+      const float* row = xbc + (size_t)(start + t0 + tt) * xbc_stride;
+      Bs[tt * N + n] = row[inner + g * N + n];
+      Cs[tt * N + n] = row[inner + groups * N + g * N + n];
+    }
+    for (int i = tid; i < nt * SCAN_PB; i += SCAN_THREADS) {
+      const int tt = i / SCAN_PB, pp = i - tt * SCAN_PB;
+      xs[i] = p0 + pp < P ? xbc[(size_t)(start + t0 + tt) * xbc_stride + h * P + p0 + pp] : 0.f;
+    }
+    if (tid < nt) {
+      const float v = to_f32<T>(dt_raw[(size_t)(start + t0 + tid) * dt_stride + h]) + bias;
+      const float dt = v > 20.f ? v : log1pf(expf(v));
+      dts[tid] = dt;
+      decs[tid] = expf(a * dt);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float dt = dts[tt], dec = decs[tt];
+      const float xv = xs[tt * SCAN_PB + pl];
+      const float dx = dt * xv;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const int n = lane + SCAN_LANES * i;
+        if (n < N) {
+          s[i] = fmaf(dec, s[i], Bs[tt * N + n] * dx);
+          acc = fmaf(s[i], Cs[tt * N + n], acc);
+        }
+      }
+#pragma unroll
+      for (int o = SCAN_LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0 && p_ok) y[(size_t)(start + t0 + tt) * y_stride + h * P + p] = fmaf(dsk, xv, acc);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = lane + SCAN_LANES * i;
+    if (p_ok && n < N) S[(size_t)n * P + p] = s[i];
+  }
+}
+
+// ---- gate, then RMS norm in equal parts ---------------------------------------------------------
+// out[t, part] = v * rsqrt(mean(v^2) + eps) * w with v = y * silu(z) over the part's columns.
+constexpr int GN_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(GN_THREADS)
+gated_part_norm_kernel(const float* __restrict__ y, long y_stride, const T* __restrict__ z, long z_stride,
+                       const float* __restrict__ w, T* __restrict__ out, long out_stride, const int* __restrict__ req,
+                       int part, float eps) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, c0 = blockIdx.y * part;
+  if (req[t] < 0) return;
+  const float* yr = y + (size_t)t * y_stride + c0;
+  const T* zr = z + (size_t)t * z_stride + c0;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < part; d += GN_THREADS) {
+    const float zv = to_f32<T>(zr[d]);
+    const float v = yr[d] * (zv / (1.f + expf(-zv)));
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)part + eps);
+  for (int d = threadIdx.x; d < part; d += GN_THREADS) {
+    const float zv = to_f32<T>(zr[d]);
+    const float v = yr[d] * (zv / (1.f + expf(-zv)));
+    out[(size_t)t * out_stride + c0 + d] = from_f32<T>(v * rstd * w[c0 + d]);
+  }
+}
+
+// ---- C interface -----------------------------------------------------------------------------------
+
+extern "C" int fg_mamba2_conv(const void* proj, long proj_stride, long xbc_offset, int dtype, float* out,
+                              long out_stride, const float* w, const float* bias, float* state, long state_stride,
+                              long conv_offset, const int* req, const int* seq_slot, const int* seq_start,
+                              int n_tokens, int n_seqs, int channels, int taps, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(taps >= 1 && taps <= CONV_MAX_TAPS, "fg_mamba2_conv: %d taps (1 to %d)", taps, CONV_MAX_TAPS);
+  const dim3 grid((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels + CONV_THREADS - 1) / CONV_THREADS);
+  const dim3 sgrid(n_seqs, grid.y);
+  if (dtype == FG_F32) {
+    const float* in = (const float*)proj + xbc_offset;
+    conv_silu_kernel<float><<<grid, CONV_THREADS, 0, stream>>>(in, proj_stride, out, out_stride, w,
+                                                               bias, state, state_stride, conv_offset,
+                                                               req, n_tokens, channels, taps);
+    FG_CHECK_LAUNCH("fg_mamba2_conv");
+    if (taps > 1)
+      conv_state_kernel<float><<<sgrid, CONV_THREADS, 0, stream>>>(in, proj_stride, state, state_stride, conv_offset,
+                                                                   seq_slot, seq_start, channels, taps);
+  } else if (dtype == FG_BF16) {
+    const __nv_bfloat16* in = (const __nv_bfloat16*)proj + xbc_offset;
+    conv_silu_kernel<__nv_bfloat16><<<grid, CONV_THREADS, 0, stream>>>(
+        in, proj_stride, out, out_stride, w, bias, state, state_stride,
+        conv_offset, req, n_tokens, channels, taps);
+    FG_CHECK_LAUNCH("fg_mamba2_conv");
+    if (taps > 1)
+      conv_state_kernel<__nv_bfloat16><<<sgrid, CONV_THREADS, 0, stream>>>(
+          in, proj_stride, state, state_stride, conv_offset, seq_slot, seq_start, channels, taps);
+  } else {
+    FG_CHECK_ARG(false, "fg_mamba2_conv: bad dtype %d", dtype);
+  }
+  FG_CHECK_LAUNCH("fg_mamba2_conv (state)");
+  return 0;
+}
+
+template <typename T>
+static int launch_scan(const float* xbc, long xbc_stride, const T* dt_raw, long dt_stride, const float* dt_bias,
+                       const float* a_log, const float* d_skip, float* y, long y_stride, float* state, long state_stride,
+                       const int* seq_slot, const int* seq_start, int n_seqs, int heads, int groups, int N, int P,
+                       cudaStream_t stream) {
+  const dim3 grid(n_seqs, heads, (P + SCAN_PB - 1) / SCAN_PB);
+  const size_t smem = sizeof(float) * (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS);
+  const int npt = (N + SCAN_LANES - 1) / SCAN_LANES;
+#define SCAN(NPT)                                                                                               \
+  do {                                                                                                          \
+    if (smem > 48 * 1024)                                                                                       \
+      cudaFuncSetAttribute(ssm_scan_kernel<T, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    ssm_scan_kernel<T, NPT><<<grid, SCAN_THREADS, smem, stream>>>(xbc, xbc_stride, dt_raw, dt_stride, dt_bias,  \
+                                                                  a_log, d_skip, y, y_stride, state,            \
+                                                                  state_stride, seq_slot, seq_start, heads,     \
+                                                                  groups, N, P);                                \
+  } while (0)
+  if (npt <= 1) SCAN(1);
+  else if (npt <= 2) SCAN(2);
+  else if (npt <= 4) SCAN(4);
+  else if (npt <= 8) SCAN(8);
+  else if (npt <= 16) SCAN(16);
+  else if (npt <= 32) SCAN(32);
+  else {
+    fg_set_error("fg_mamba2_scan: a state of %d rows is more than the kernel takes (256)", N);
+    return -1;
+  }
+#undef SCAN
+  return 0;
+}
+
+extern "C" int fg_mamba2_scan(const float* xbc, long xbc_stride, const void* proj, long proj_stride, long dt_offset,
+                              int dtype, const float* dt_bias, const float* a_log, const float* d_skip, float* y,
+                              long y_stride, float* state, long state_stride, const int* seq_slot,
+                              const int* seq_start, int n_seqs, int heads, int groups, int N, int P,
+                              cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  FG_CHECK_ARG(heads > 0 && groups > 0 && heads % groups == 0 && N > 0 && P > 0,
+               "fg_mamba2_scan: bad sizes heads=%d groups=%d N=%d P=%d", heads, groups, N, P);
+  int rc;
+  if (dtype == FG_F32)
+    rc = launch_scan<float>(xbc, xbc_stride, (const float*)proj + dt_offset, proj_stride, dt_bias,
+                            a_log, d_skip, y, y_stride, state, state_stride, seq_slot,
+                            seq_start, n_seqs, heads, groups, N, P, stream);
+  else if (dtype == FG_BF16)
+    rc = launch_scan<__nv_bfloat16>(xbc, xbc_stride, (const __nv_bfloat16*)proj + dt_offset, proj_stride,
+                                    dt_bias, a_log, d_skip, y, y_stride, state, state_stride, seq_slot,
+                                    seq_start, n_seqs, heads, groups, N, P, stream);
+  else
+    FG_CHECK_ARG(false, "fg_mamba2_scan: bad dtype %d", dtype);
+  if (rc) return rc;
+  FG_CHECK_LAUNCH("fg_mamba2_scan");
+  return 0;
+}
+
+extern "C" int fg_gated_part_norm(const float* y, long y_stride, const void* z, long z_stride, int dtype,
+                                  const float* w, void* out, long out_stride, const int* req, int n_tokens, int width,
+                                  int parts, float eps, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(parts > 0 && width % parts == 0, "fg_gated_part_norm: %d columns in %d parts", width, parts);
+  const dim3 grid(n_tokens, parts);
+  if (dtype == FG_F32)
+    gated_part_norm_kernel<float><<<grid, GN_THREADS, 0, stream>>>(y, y_stride, (const float*)z, z_stride,
+                                                                    w, (float*)out, out_stride, req,
+                                                                    width / parts, eps);
+  else if (dtype == FG_BF16)
+    gated_part_norm_kernel<__nv_bfloat16><<<grid, GN_THREADS, 0, stream>>>(
+        y, y_stride, (const __nv_bfloat16*)z, z_stride, w, (__nv_bfloat16*)out, out_stride, req,
+        width / parts, eps);
+  else
+    FG_CHECK_ARG(false, "fg_gated_part_norm: bad dtype %d", dtype);
+  FG_CHECK_LAUNCH("fg_gated_part_norm");
+  return 0;
+}

@@ -39,9 +39,19 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 _P, _I, _F = c_void_p, c_int, c_float
+_L = ctypes.c_long
 
 _CORE_SIGNATURES = {
-    "fg_embedding": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fg_embedding": [_P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
+    "fg_stream_norm": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _I, _P],
+    "fg_mamba2_conv": [_P, _L, _L, _I, _P, _L, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fg_mamba2_scan": [_P, _L, _P, _L, _L, _I, _P, _P, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fg_gated_part_norm": [_P, _L, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _F, _P],
+    "fg_rms_rows": [_P, _L, _I, _P, _F, _P, _L, _I, _I, _P],
+    "fg_rotate_part": [_P, _L, _I, _P, _P, _P, _F, _I, _I, _I, _I, _I, _P],
+    "fg_latent_entry_write": [_P, _L, _I, _P, _F, _P, _F, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fg_latent_attention_simt": [_P, _I, _L, _L, _P, _L, _L, _P, _L, _L, _I, _P, _L, _P, _P, _I, _I, _I, _P, _P, _P,
+                                 _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_rmsnorm": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P],
     "fg_silu_gate": [_P, _P, _I, _I, _I, _I, _P],
     "fg_embedding_bigram": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -61,7 +71,8 @@ _CORE_SIGNATURES = {
 }
 
 _ATTN_SIGNATURES = {
-    "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
+                          _P],
     "fg_attention_sigmoid": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                              _P, _P, _P, _P, _P],
     "fg_attention_sigmoid_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I,
@@ -258,12 +269,166 @@ class Ops:
         return out.tolist()
 
     # -- kernels ---------------------------------------------------------------
-    def embedding(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    def embedding(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """``out[t] = table[tokens[t]] * scale``; an ``out`` of [T, S, dim] receives the row S times."""
         assert table.is_contiguous() and out.is_contiguous() and tokens.dtype == torch.int32
-        n, dim = out.shape
+        n, dim = out.shape[0], out.shape[-1]
+        copies = out.shape[1] if out.dim() == 3 else 1
         _check(self.lib, self.lib.fg_embedding(
             _ptr(table), _code(table.dtype), _ptr(tokens), _ptr(out), _code(out.dtype),
-            n, dim, table.shape[0], _ptr(self.status), _stream()))
+            n, dim, table.shape[0], float(scale), copies, _ptr(self.status), _stream()))
+        return out
+
+    def stream_norm(self, h, weight, bias, eps: float, out, kind: int = 0, update=None, in_coef=None, rows=None):
+        """Norm over one or several residual streams ``h`` [T, S, dim] or [T, dim] (float32), fused
+        with the update that precedes it: with ``update`` (``delta`` [T, dim], ``mix`` [S, S] or
+        ``None`` for the identity, ``out`` [S] or ``None`` for ones) every stream becomes
+        ``sum_s mix[s, t] x_s + out[t] delta``; then ``out = norm(sum_s in_coef[s] x_s)`` (``in_coef``
+        ``None``: the plain sum).  ``kind`` 0 is the layer norm (``bias`` may be ``None``), 1 the RMS
+        norm.  With ``rows`` only those rows are computed and ``h`` stays as it was."""
+        assert h.is_contiguous() and h.dtype == torch.float32
+        dim = h.shape[-1]
+        streams = h.shape[1] if h.dim() == 3 else 1
+        n = h.shape[0] if rows is None else rows.numel()
+        delta = mix = out_coef = None
+        if update is not None:
+            delta, mix, out_coef = update.delta, update.mix, update.out
+            assert delta.is_contiguous() and delta.shape == (h.shape[0], dim)
+        for t, shape in ((mix, (streams, streams)), (out_coef, (streams,)), (in_coef, (streams,)),
+                         (weight, (dim,)), (bias, (dim,))):
+            assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == shape)
+        assert out.is_contiguous() and out.shape == (n, dim)
+        assert rows is None or rows.dtype == torch.int32
+        _check(self.lib, self.lib.fg_stream_norm(
+            _ptr(h), streams, _ptr(delta), _code(delta.dtype) if delta is not None else 0, _ptr(mix), _ptr(out_coef),
+            _ptr(in_coef), _ptr(weight), _ptr(bias), _ptr(out), _code(out.dtype), _ptr(rows), n, dim, float(eps),
+            int(kind), _stream()))
+        return out
+
+    # -- the state-space mixer --------------------------------------------------------------------
+    def mamba2_conv(self, proj, xbc_offset: int, channels: int, weight, bias, state, conv_offset: int, taps: int,
+                    ctx) -> torch.Tensor:
+        """Causal convolution per channel with SiLU over the columns ``xbc_offset .. + channels`` of
+        ``proj`` [T, .]; the inputs before the step's tokens come from ``state`` [slots, .] (float32,
+        ``taps - 1`` rows of ``channels`` from ``conv_offset``), which is advanced.  Returns float32
+        [T, channels]."""
+        t = proj.shape[0]
+        assert proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+        assert weight.dtype == torch.float32 and weight.shape == (channels, taps) and weight.is_contiguous()
+        out = torch.empty((t, channels), dtype=torch.float32, device=proj.device)
+        _check(self.lib, self.lib.fg_mamba2_conv(
+            _ptr(proj), proj.stride(0), int(xbc_offset), _code(proj.dtype), _ptr(out), out.stride(0), _ptr(weight),
+            _ptr(bias), _ptr(state), state.stride(0), int(conv_offset), _ptr(ctx.req), _ptr(ctx.seq_slot),
+            _ptr(ctx.seq_start), t, ctx.n_seqs, channels, taps, _stream()))
+        Ops.launches += int(taps > 1)
+        return out
+
+    def mamba2_scan(self, xbc, proj, dt_offset: int, dt_bias, a_log, d_skip, state, ctx, heads: int, groups: int,
+                    n_state: int, head_dim: int) -> torch.Tensor:
+        """The recurrence ``S <- exp(-exp(A) dt) S + dt B x^T; y = S^T C + D x`` per (sequence, head),
+        token by token in float32, from and into ``state`` [slots, .] (its first
+        ``heads * n_state * head_dim`` numbers).  ``xbc`` [T, x | B | C] float32; the raw step sizes are
+        the columns ``dt_offset .. + heads`` of ``proj``.  Returns y [T, heads * head_dim] float32."""
+        t = xbc.shape[0]
+        assert xbc.dtype == torch.float32 and xbc.stride(1) == 1 and proj.stride(1) == 1
+        for v in (dt_bias, a_log, d_skip):
+            assert v.dtype == torch.float32 and v.numel() == heads and v.is_contiguous()
+        y = torch.empty((t, heads * head_dim), dtype=torch.float32, device=xbc.device)
+        _check(self.lib, self.lib.fg_mamba2_scan(
+            _ptr(xbc), xbc.stride(0), _ptr(proj), proj.stride(0), int(dt_offset), _code(proj.dtype), _ptr(dt_bias),
+            _ptr(a_log), _ptr(d_skip), _ptr(y), y.stride(0), _ptr(state), state.stride(0), _ptr(ctx.seq_slot),
+            _ptr(ctx.seq_start), ctx.n_seqs, heads, groups, n_state, head_dim, _stream()))
+        return y
+
+    def gated_part_norm(self, y, z, weight, parts: int, eps: float, ctx) -> torch.Tensor:
+        """``v = y * silu(z)``, RMS-normed in ``parts`` equal parts of the columns, times ``weight``;
+        ``y`` float32, ``z`` a (strided) view of the compute dtype, which the result has."""
+        t, width = y.shape
+        assert y.dtype == torch.float32 and y.stride(1) == 1 and z.stride(1) == 1 and z.shape == (t, width)
+        assert weight.dtype == torch.float32 and weight.numel() == width and weight.is_contiguous()
+        out = torch.empty((t, width), dtype=z.dtype, device=y.device)
+        _check(self.lib, self.lib.fg_gated_part_norm(
+            _ptr(y), y.stride(0), _ptr(z), z.stride(0), _code(z.dtype), _ptr(weight), _ptr(out), out.stride(0),
+            _ptr(ctx.req), t, width, parts, float(eps), _stream()))
+        return out
+
+    # -- latent attention ---------------------------------------------------------------------------
+    def rms_rows(self, x, weight, eps: float) -> torch.Tensor:
+        """``x * rsqrt(mean(x^2) + eps) * weight`` per row of ``x`` [T, dim], which may be a column
+        range of a wider tensor; float32 arithmetic, the result has ``x``'s type."""
+        assert x.stride(1) == 1 and weight.dtype == torch.float32 and weight.numel() == x.shape[1]
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        _check(self.lib, self.lib.fg_rms_rows(_ptr(x), x.stride(0), _code(x.dtype), _ptr(weight), float(eps),
+                                              _ptr(out), out.stride(0), x.shape[0], x.shape[1], _stream()))
+        return out
+
+    def head_products(self, x, w, w_t=None, out=None) -> torch.Tensor:
+        """One product per head: ``out[h] = x[:, h, :] @ w[h]`` for ``x`` [T, H, a] (a strided view),
+        ``w`` [H, a, b]; returns [H, T, b].  bfloat16 is the library's batched product; float32 runs
+        this package's float32 product head by head and wants ``w_t`` [H, b, a]."""
+        t, H, a = x.shape
+        b = w.shape[2]
+        if out is None:
+            out = torch.empty((H, t, b), dtype=x.dtype, device=x.device)
+        if x.dtype == torch.bfloat16:
+            torch.bmm(x.permute(1, 0, 2), w, out=out)
+            return out
+        assert w_t is not None and w_t.shape == (H, b, a) and x.stride(2) == 1
+        for h in range(H):
+            self.linear(x[:, h, :], w_t[h], out=out[h])
+        return out
+
+    def head_products_out(self, x, w, w_t, out) -> torch.Tensor:
+        """``out[:, h, :] = x[h] @ w[h].T`` for ``x`` [H, T, a], ``w`` [H, b, a] (``w_t`` [H, a, b] for
+        the library's batched product in bfloat16), ``out`` [T, H, b]: heads side by side."""
+        H = x.shape[0]
+        if x.dtype == torch.bfloat16:
+            torch.bmm(x, w_t, out=out.permute(1, 0, 2))
+            return out
+        for h in range(H):
+            self.linear(x[h], w[h], out=out[:, h, :])
+        return out
+
+    def rotate_part(self, x, ctx, freqs, magnitude: float, n_heads: int, head_size: int, offset: int,
+                    rot_dims: int) -> torch.Tensor:
+        """Turn, in place, the adjacent pairs of the dimensions ``offset .. + rot_dims`` of every head of
+        ``x`` [T, heads * head_size] by ``pos * freqs``; cosine and sine are multiplied by ``magnitude``."""
+        assert x.stride(1) == 1 and freqs.dtype == torch.float32 and freqs.numel() >= rot_dims // 2
+        _check(self.lib, self.lib.fg_rotate_part(
+            _ptr(x), x.stride(0), _code(x.dtype), _ptr(ctx.pos), _ptr(ctx.req), _ptr(freqs), float(magnitude),
+            x.shape[0], n_heads, head_size, offset, rot_dims, _stream()))
+        return x
+
+    def latent_entry_write(self, src, norm_weight, eps: float, freqs, magnitude: float, memory, ctx, rank: int,
+                           rot_dim: int) -> None:
+        """The cache entries of the step's tokens: ``[rmsnorm(src[:, :rank]) * w | src[:, rank:] turned]``
+        into the pages of ``memory`` (one pool, one head, entries of ``head_dim`` numbers)."""
+        pages = memory.k_pages
+        assert src.stride(1) == 1 and src.shape[1] == rank + rot_dim and pages.is_contiguous()
+        assert norm_weight.dtype == torch.float32 and norm_weight.numel() == rank
+        _check(self.lib, self.lib.fg_latent_entry_write(
+            _ptr(src), src.stride(0), _code(src.dtype), _ptr(norm_weight), float(eps), _ptr(freqs), float(magnitude),
+            _ptr(pages), _ptr(memory.block_table), memory.block_table.shape[1], memory.page_size, pages.shape[0],
+            _ptr(ctx.pos), _ptr(ctx.req), src.shape[0], rank, rot_dim, pages.shape[-1], _ptr(self.status),
+            _stream()))
+
+    def latent_attention(self, qa, qt, out, gate, memory, ctx, n_heads: int, rank: int, rot_dim: int,
+                         scale: float) -> torch.Tensor:
+        """Causal softmax attention of ``n_heads`` query heads on the one cached entry per token:
+        score ``(qa_h . c + qt_h . k_t) * scale``, output the weighted sum of the latents ``c``, times
+        ``sigmoid(gate[t, h])`` when a gate is given.  ``qa`` [heads, T, rank] (folded queries),
+        ``qt`` [T, heads, rot_dim] (a strided view), ``out`` [heads, T, rank], ``gate`` [T, heads]
+        (a strided view) or ``None``."""
+        pages = memory.k_pages
+        assert qa.stride(2) == 1 and qt.stride(2) == 1 and out.stride(2) == 1 and pages.is_contiguous()
+        assert gate is None or gate.stride(1) == 1
+        tiles = ctx.attention_tiles(attention_tiling(n_heads, 1, SIMT_ROWS), 1)
+        _check(self.lib, self.lib.fg_latent_attention_simt(
+            _ptr(qa), _code(qa.dtype), qa.stride(1), qa.stride(0), _ptr(qt), qt.stride(0), qt.stride(1), _ptr(out),
+            out.stride(1), out.stride(0), _code(out.dtype), _ptr(gate), gate.stride(0) if gate is not None else 0,
+            _ptr(pages), _ptr(memory.block_table), memory.block_table.shape[1], memory.page_size, pages.shape[0],
+            _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, n_heads, rank, rot_dim,
+            pages.shape[-1], float(scale), _ptr(self.status), _stream()))
         return out
 
     def embedding_bigram(self, table, bigram, tokens, pos, req, last_token, out, buckets: int, mul_prev: int,
@@ -506,7 +671,8 @@ class Ops:
         return scratch, flags, room
 
     def attention(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
-                  window: Optional[int], scale: float, out_freqs: Optional[torch.Tensor] = None) -> bool:
+                  window: Optional[int], scale: float, out_freqs: Optional[torch.Tensor] = None,
+                  keep_first: int = 0) -> bool:
         """Paged causal attention of the step's query tokens; ``memory`` is the
         run's :class:`~fastgen_b200.cache.LayerMemory`, ``ctx`` the step's
         context.  bfloat16 runs on the tensor cores: prompt portions in one
@@ -523,12 +689,14 @@ class Ops:
         assert q.stride(1) == 1 and out.stride(1) == 1
         common = (_ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
                   k_pages.shape[0], _ptr(ctx.pos))
-        if q.dtype == torch.float32:
+        keep_first = int(keep_first) if window else 0
+        if q.dtype == torch.float32 or keep_first:
+            # float32, and windows that keep a sequence's first positions visible: the CUDA-core kernel
             tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, SIMT_ROWS), 1)
             _check(lib, lib.fg_attention_simt(
-                _ptr(q), q.stride(0), _ptr(out), out.stride(0), FG_F32, *common,
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), *common,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
-                n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
+                n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale),
                 _ptr(self.status), _stream()))
             return False
         use_tma = memory.tensor_maps is not None

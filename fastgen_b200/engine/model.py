@@ -20,7 +20,9 @@ from ..parts.base import (
     Embedder,
     StateSpec,
     WeightSpec,
+    StreamUpdate,
     make_block,
+    make_connection,
     make_embedder,
     make_feed_forward,
     make_mixer,
@@ -31,7 +33,7 @@ from ..parts.params import TableEmbeddingParams
 from ..weights.loader import load_weights
 
 
-_MAKERS = {"mixer": make_mixer, "norm": make_norm, "feed_forward": make_feed_forward}
+_MAKERS = {"mixer": make_mixer, "norm": make_norm, "feed_forward": make_feed_forward, "connection": make_connection}
 
 
 def _build_blocks(args: ModelArgs) -> List[Block]:
@@ -181,6 +183,12 @@ class Model:
             if spec.init[0] == "normal":
                 t = torch.empty(spec.shape, dtype=torch.bfloat16, device=device)
                 t.normal_(0.0, spec.init[1], generator=gen)
+            elif spec.init[0] == "uniform":
+                t = torch.empty(spec.shape, dtype=torch.float32, device=device)
+                t.uniform_(spec.init[1], spec.init[2], generator=gen)
+                t = t.to(torch.bfloat16)
+            elif spec.init[0] == "constant":
+                t = torch.full(spec.shape, spec.init[1], dtype=torch.bfloat16, device=device)
             elif spec.init[0] in ("ones", "ones_jitter"):
                 t = torch.ones(spec.shape, dtype=torch.bfloat16, device=device)
             else:
@@ -197,18 +205,24 @@ class Model:
         ``LayerMemory`` per schedule entry, and the state of an embedder that keeps one."""
         ops = self.ops
         t = ctx.n_tokens
-        h = torch.empty((t, self.args.dim), dtype=torch.float32, device=ops.device)
+        # one residual stream [T, dim], or several side by side [T, streams, dim] that start equal
+        shape = (t, self.args.dim) if self.args.streams is None else (t, self.args.streams, self.args.dim)
+        h = torch.empty(shape, dtype=torch.float32, device=ops.device)
         self.embedder.forward(ctx, getattr(memories, "embedder_state", None), h)
         pending = None
         for e, entry in enumerate(self.args.schedule):
             h, pending = self.blocks[entry.layer].forward(h, pending, ctx, memories[e])
         if ctx.n_want == 0:
             return None
-        delta, delta_norm = split_pending(pending)
-        if delta is None:
-            x = self.final_norm.forward(h, rows=ctx.want_rows)
+        if self.args.streams is not None:
+            # the last update of the streams, their sum and the norm in one kernel
+            x = self.final_norm.streams_forward(h, update=pending, rows=ctx.want_rows)
         else:
-            x = self.final_norm.add_forward(h, delta, rows=ctx.want_rows, delta_norm=delta_norm)
+            delta, delta_norm = split_pending(pending)
+            if delta is None:
+                x = self.final_norm.forward(h, rows=ctx.want_rows)
+            else:
+                x = self.final_norm.add_forward(h, delta, rows=ctx.want_rows, delta_norm=delta_norm)
         logits = ops.linear(x, self.output, out_dtype=torch.float32)
         if self.args.logit_scale != 1.0 or self.args.logit_softcap:
             ops.scale_softcap(logits, self.args.logit_scale, self.args.logit_softcap)

@@ -96,7 +96,7 @@ class GQAAttention(Mixer):
 
     def cache_spec(self) -> Optional[CacheSpec]:
         p = self.params
-        return CacheSpec(p.n_kv_heads, self.hd, p.window)
+        return CacheSpec(p.n_kv_heads, self.hd, p.window, keep_first=p.keep_first if p.window else 0)
 
     def _rot_dims(self, position, size: int) -> int:
         params = getattr(position, "params", None)
@@ -150,7 +150,7 @@ class GQAAttention(Mixer):
         back already (values cached turned by their positions): the kernels do it where they can."""
         p = self.params
         return self.ops.attention(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale,
-                                  out_freqs=self.v_unfreqs)
+                                  out_freqs=self.v_unfreqs, keep_first=p.keep_first)
 
     def forward(self, x, ctx, memory):
         p, ops = self.params, self.ops

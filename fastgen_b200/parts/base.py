@@ -50,6 +50,7 @@ class CacheSpec:
     window: Optional[int] = None  # keys a query may see, itself included
     n_pools: int = 2  # 2: keys and values; 1: one entry per token
     page_size: Optional[int] = None  # tokens per page; None: the engine's page size
+    keep_first: int = 0  # with a window: a sequence's first positions that stay visible for good
 
     def __post_init__(self) -> None:
         if self.n_pools not in (1, 2):
@@ -121,6 +122,18 @@ class NormedDelta:
     norm: Optional[Norm] = None
 
 
+@dataclass
+class StreamUpdate:
+    """A sub-layer's output on its way into several residual streams: every stream becomes a
+    mix of the old streams plus its own multiple of ``delta``
+    (``x_t <- sum_s mix[s, t] x_s + out[t] delta``; ``None`` stands for the identity mix and for
+    ones).  Handed on as ``pending`` so that the update is fused with the next read."""
+
+    delta: torch.Tensor
+    mix: Optional[torch.Tensor] = None
+    out: Optional[torch.Tensor] = None
+
+
 def split_pending(pending):
     """``(delta, its norm)`` of what a block handed on: a tensor, a :class:`NormedDelta` or ``None``."""
     if isinstance(pending, NormedDelta):
@@ -179,6 +192,20 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """How a sub-layer is wired to the residual stream(s) ``h`` [T, streams, dim].
+
+    ``read`` applies what the sub-layer before left pending, forms this sub-layer's input from
+    the streams and returns its norm; ``write`` wraps the sub-layer's output as the pending
+    update of the streams."""
+
+    def read(self, h: torch.Tensor, pending, norm: "Norm") -> torch.Tensor:
+        raise NotImplementedError
+
+    def write(self, delta: torch.Tensor):
+        raise NotImplementedError
+
+
 class Block:
     """Arrangement of a layer's parts around the residual stream."""
 
@@ -208,6 +235,15 @@ _NORMS: Dict[str, Callable[[PartSpec], Norm]] = {}
 _POSITIONS: Dict[str, Callable[[PartSpec], PositionEncoding]] = {}
 _BLOCKS: Dict[str, Callable[..., Block]] = {}
 _EMBEDDERS: Dict[str, Callable[[PartSpec], Embedder]] = {}
+_CONNECTIONS: Dict[str, Callable[[PartSpec], Connection]] = {}
+
+
+def register_connection(kind: str, factory) -> None:
+    _CONNECTIONS[kind] = factory
+
+
+def make_connection(spec: PartSpec) -> Connection:
+    return _make(_CONNECTIONS, "connection", spec)
 
 
 def register_embedder(kind: str, factory) -> None:

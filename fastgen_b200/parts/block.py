@@ -17,6 +17,8 @@ class PreNormBlock(Block):
         delta, delta_norm = split_pending(pending)
         a = self.mixer_norm.add_forward(h, delta, delta_norm=delta_norm)
         m = self.mixer.forward(a, ctx, memory)
+        if self.ffn is None:  # a layer of one sub-layer
+            return h, m
         f = self.ffn_norm.add_forward(h, m)
         return h, self.ffn.forward(f, ctx)
 
@@ -42,5 +44,22 @@ class SandwichBlock(Block):
         return h, NormedDelta(self.ffn.forward(f, ctx), self.extra.get("post_ffn_norm"))
 
 
+class StreamsBlock(Block):
+    """Pre-norm sub-layers on several residual streams: ``h`` is [T, streams, dim] and every
+    sub-layer reads and writes it through a connection of its own, the extra parts
+    ``mixer_connection`` and ``ffn_connection``.  What a sub-layer writes stays pending until the
+    next read, whose kernel applies it.  A layer without a feed-forward ends after the mixer."""
+
+    def forward(self, h, pending, ctx, memory):
+        c = self.extra["mixer_connection"]
+        m = self.mixer.forward(c.read(h, pending, self.mixer_norm), ctx, memory)
+        pending = c.write(m)
+        if self.ffn is None:
+            return h, pending
+        c = self.extra["ffn_connection"]
+        return h, c.write(self.ffn.forward(c.read(h, pending, self.ffn_norm), ctx))
+
+
 register_block("prenorm", PreNormBlock)
+register_block("streams", StreamsBlock)
 register_block("sandwich", SandwichBlock)

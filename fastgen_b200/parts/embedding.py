@@ -11,7 +11,8 @@ from .params import BigramHashParams, TableEmbeddingParams
 
 
 class TableEmbedding(Embedder):
-    """``x = table[token]`` (F.embedding of fastgen/forward.py:403-410)."""
+    """``x = table[token] * scale`` (F.embedding of fastgen/forward.py:403-410; the scale is a
+    float32 product).  An output of [T, S, dim] receives the row S times."""
 
     params: TableEmbeddingParams
 
@@ -27,7 +28,7 @@ class TableEmbedding(Embedder):
         return self.weight
 
     def forward(self, ctx, state, out):
-        return self.ops.embedding(self.weight, ctx.tokens, out)
+        return self.ops.embedding(self.weight, ctx.tokens, out, scale=self.params.scale)
 
 
 class BigramHashEmbedding(Embedder):

@@ -6,8 +6,8 @@ from typing import List
 
 import torch
 
-from .base import Norm, WeightSpec, register_norm
-from .params import DynamicTanhParams, RMSNormParams
+from .base import Norm, StreamUpdate, WeightSpec, register_norm
+from .params import DynamicTanhParams, LayerNormParams, RMSNormParams
 
 
 class RMSNorm(Norm):
@@ -88,5 +88,49 @@ class DynamicTanh(Norm):
         return self.ops.dyt(h, self.triple(), out, delta=delta, post=post, rows=rows)
 
 
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w + b`` in float32; the variance is the mean of the squared
+    deviations.  Tensors ``weight`` and, with ``params.bias``, ``bias``.
+
+    The residual stream may be several streams ``h`` [T, S, dim] that are mixed on the way
+    (``streams_forward``): the update a sub-layer left pending, the weighted sum of the streams
+    and the norm are one kernel.  The plain ``h += delta; norm(h)`` is its case ``S = 1``."""
+
+    params: LayerNormParams
+    kind = 0  # the kernel's code for "with mean and variance"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        d = self.params.dim
+        specs = [WeightSpec(self.names["weight"], (d,), ("ones",))]
+        if self.params.bias:
+            specs.append(WeightSpec(self.names["bias"], (d,), ("normal", 0.02)))
+        return specs
+
+    def bind(self, tensors, ops) -> None:
+        self.ops = ops
+        self.weight = tensors["weight"].float().contiguous()
+        self.bias = tensors["bias"].float().contiguous() if self.params.bias else None
+
+    def streams_forward(self, h, update=None, in_coef=None, rows=None, out_dtype=None):
+        """``h`` [T, S, dim] (or [T, dim]): apply ``update`` (a :class:`StreamUpdate` or ``None``),
+        then norm ``sum_s in_coef[s] x_s`` (``in_coef`` ``None``: the plain sum)."""
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, h.shape[-1]), dtype=out_dtype or self.ops.act_dtype, device=h.device)
+        return self.ops.stream_norm(h, self.weight, self.bias, self.params.eps, out, kind=self.kind, update=update,
+                                    in_coef=in_coef, rows=rows)
+
+    def forward(self, x, out_dtype=None, rows=None):
+        if x.dtype != torch.float32:
+            x = x.float()
+        return self.streams_forward(x, rows=rows, out_dtype=out_dtype)
+
+    def add_forward(self, h, delta, rows=None, delta_norm=None):
+        if delta is not None and delta_norm is not None:
+            delta = delta_norm.forward(delta, out_dtype=torch.float32)
+        update = StreamUpdate(delta) if delta is not None else None
+        return self.streams_forward(h, update=update, rows=rows)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)
 register_norm("dynamic_tanh", DynamicTanh)

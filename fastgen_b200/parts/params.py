@@ -22,6 +22,22 @@ class Llama3Scaling:
 
 
 @dataclass(frozen=True)
+class YarnScaling:
+    """Frequency interpolation by parts with a ramp between two pair indices ("YaRN").
+
+    With ``dim(t) = dims * ln(original / (2 pi t)) / (2 ln theta)`` the ramp runs from
+    ``lo = max(floor(dim(fast)), 0)`` to ``hi = min(ceil(dim(slow)), dims - 1)``:
+    ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` and pair ``i`` turns with
+    ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``.  Cosine and sine are both multiplied by
+    ``0.1 * ln(factor) + 1`` (the encoding's ``magnitude``)."""
+
+    factor: float
+    original_max_positions: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class RopeParams:
     """Rotary position encoding over adjacent pairs (fastgen/kernels/rope.py:77-89).
 
@@ -33,7 +49,7 @@ class RopeParams:
 
     head_dim: int
     theta: float
-    scaling: Optional[Llama3Scaling] = None
+    scaling: Optional[object] = None  # a Llama3Scaling or a YarnScaling
     rot_dims: Optional[int] = None
     linear_factor: Optional[float] = None
 
@@ -81,6 +97,9 @@ class AttentionParams:
     #: head's dimensions, as ``qk_layout`` is for queries and keys.
     value_position: Optional[object] = None
     v_layout: str = "adjacent"
+    #: with a window: so many of a sequence's first positions stay visible to every later
+    #: query, at their true positions
+    keep_first: int = 0
 
     def __post_init__(self) -> None:
         for name, layout in (("qk_layout", self.qk_layout), ("v_layout", self.v_layout)):
@@ -102,6 +121,8 @@ class AttentionParams:
                 raise ValueError(f"head size {size} is odd: a rotation needs pairs of dimensions")
         if self.window is not None and self.window <= 0:
             raise ValueError(f"attention window must be positive, got {self.window}")
+        if self.keep_first < 0:
+            raise ValueError(f"the number of first positions kept visible cannot be negative, got {self.keep_first}")
 
     @property
     def kernel_head_dim(self) -> int:
@@ -160,10 +181,11 @@ class DynamicTanhParams:
 
 @dataclass(frozen=True)
 class TableEmbeddingParams:
-    """``x = table[token]``."""
+    """``x = table[token] * scale``."""
 
     vocab_size: int
     dim: int
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -180,3 +202,91 @@ class BigramHashParams:
     def __post_init__(self) -> None:
         if self.buckets <= 0:
             raise ValueError(f"a bigram table needs at least one bucket, got {self.buckets}")
+
+
+@dataclass(frozen=True)
+class LayerNormParams:
+    """``(x - mean) / sqrt(var + eps) * w + b`` with the variance the mean of the squared
+    deviations; ``bias`` says whether the norm has a ``b``."""
+
+    dim: int
+    eps: float
+    bias: bool = True
+
+
+@dataclass(frozen=True)
+class HyperConnectionParams:
+    """How a sub-layer reads from and writes to ``streams`` residual streams: its input is
+    ``sum_s in[s] x_s`` and, with its output ``y``, ``x_t <- sum_s mix[s, t] x_s + out[t] y``."""
+
+    streams: int
+
+    def __post_init__(self) -> None:
+        if not 1 <= self.streams <= 8:
+            raise ValueError(f"1 to 8 residual streams are supported, got {self.streams}")
+
+
+@dataclass(frozen=True)
+class Mamba2Params:
+    """State-space mixer in the Mamba-2 form: ``n_heads`` heads of ``head_dim`` values, a state of
+    ``state`` rows per head, ``groups`` groups of heads that share B and C, a causal convolution
+    of ``conv`` taps over x, B and C, and a gated RMS norm in ``norm_groups`` equal parts."""
+
+    dim: int
+    n_heads: int
+    head_dim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+    eps: float
+
+    def __post_init__(self) -> None:
+        if self.n_heads % self.groups:
+            raise ValueError(f"{self.n_heads} heads cannot be split into {self.groups} groups")
+        if (self.n_heads * self.head_dim) % self.norm_groups:
+            raise ValueError(f"{self.n_heads * self.head_dim} columns cannot be normed in {self.norm_groups} equal parts")
+        if not 1 <= self.conv <= 8:
+            raise ValueError(f"the convolution takes 1 to 8 taps, got {self.conv}")
+        if not 1 <= self.state <= 256:
+            raise ValueError(f"the state takes 1 to 256 rows, got {self.state}")
+
+    @property
+    def inner(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def channels(self) -> int:
+        """Columns that pass the convolution: x, B and C."""
+        return self.inner + 2 * self.groups * self.state
+
+
+@dataclass(frozen=True)
+class LatentAttentionParams:
+    """Causal softmax attention whose keys and values are linear maps of a cached latent.
+
+    Queries come through a latent of ``q_rank`` numbers (RMS-normed); a head's query and key have
+    ``head_dim`` unrotated and ``rot_dim`` rotated dimensions (``position`` is the ``PartSpec`` of
+    the rotation of those), its value ``v_head_dim``.  A token caches ``kv_rank`` latent numbers
+    (RMS-normed) and one rotated key part that all heads share.  ``own_cache`` false: the layer
+    has no latent projection and reads the entries another layer caches.  ``gate``: every head's
+    output is multiplied by the sigmoid of a projection of the mixer's input."""
+
+    dim: int
+    n_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    softmax_scale: float
+    eps: float
+    position: object
+    own_cache: bool = True
+    gate: bool = True
+
+    def __post_init__(self) -> None:
+        if self.rot_dim % 2:
+            raise ValueError(f"the rotated part has {self.rot_dim} dimensions: a rotation needs pairs")
+        if not 1 <= self.kv_rank <= 512:
+            raise ValueError(f"the attention kernels take latents of 1 to 512 numbers, got {self.kv_rank}")

@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from .base import PositionEncoding, register_position
-from .params import NoPositionParams, RopeParams
+from .params import NoPositionParams, RopeParams, YarnScaling
 
 
 def rope_frequencies(params: RopeParams) -> torch.Tensor:
@@ -29,6 +29,14 @@ def rope_frequencies(params: RopeParams) -> torch.Tensor:
     sc = params.scaling
     if sc is None:
         return freqs
+    if isinstance(sc, YarnScaling):
+        def turn_dim(turns: float) -> float:
+            return hd * math.log(sc.original_max_positions / (2 * math.pi * turns)) / (2 * math.log(params.theta))
+
+        lo = max(math.floor(turn_dim(sc.fast)), 0)
+        hi = min(math.ceil(turn_dim(sc.slow)), hd - 1)
+        ramp = ((torch.arange(hd // 2, dtype=torch.float32) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return freqs / sc.factor * ramp + freqs * (1.0 - ramp)
     wavelen = (2 * math.pi) / freqs
     low_wavelen = sc.original_max_positions / sc.low_freq_factor
     high_wavelen = sc.original_max_positions / sc.high_freq_factor
@@ -43,9 +51,16 @@ def rope_frequencies(params: RopeParams) -> torch.Tensor:
 class Rope(PositionEncoding):
     """Rotation of adjacent pairs ``(x[2j], x[2j+1])`` by ``pos * freq_j``
     (fastgen/kernels/rope.py:57-89).  The kernels are table-driven, so another
-    frequency law is another ``table()``."""
+    frequency law is another ``table()``.  ``magnitude()`` is the number cosine and sine are
+    both multiplied by (1 unless the scaling says otherwise)."""
 
     params: RopeParams
+
+    def magnitude(self) -> float:
+        sc = self.params.scaling
+        if isinstance(sc, YarnScaling):
+            return 0.1 * math.log(sc.factor) + 1.0
+        return 1.0
 
     def __init__(self, spec) -> None:
         super().__init__(spec)

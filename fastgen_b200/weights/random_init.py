@@ -29,6 +29,11 @@ def draw(spec: WeightSpec, gen: torch.Generator, norm_jitter: float = 0.0) -> to
             u = torch.rand(spec.shape, generator=gen, dtype=torch.float32)
             return 1.0 + (2.0 * u - 1.0) * norm_jitter
         return torch.ones(spec.shape, dtype=torch.float32)
+    if kind == "uniform":
+        u = torch.rand(spec.shape, generator=gen, dtype=torch.float32)
+        return spec.init[1] + (spec.init[2] - spec.init[1]) * u
+    if kind == "constant":
+        return torch.full(spec.shape, float(spec.init[1]), dtype=torch.float32)
     if kind == "randint":
         return torch.randint(0, spec.init[1], spec.shape, generator=gen, dtype=torch.int32)
     raise ValueError(f"unknown init law {spec.init!r} for {spec.name}")
