@@ -361,10 +361,11 @@ class CacheManager:
                 for lp in gone:
                     grp.host_table[req.slot, lp] = -1
                     grp.dirty.append((req.slot, lp, -1))
-                if not req.pages[gi]:
-                    # a window shorter than a page can leave a group without a page at a page's
-                    # edge: the bound says nothing then, the next reservation looks at the maps
-                    req.reserved = 0
+                # a window shorter than a page can leave a group without a page behind the kept ones
+                # at a page's edge: the bound shrinks to what the remaining pages cover, and the
+                # next reservation looks at the maps
+                held = req.pages[gi]
+                req.reserved = min(req.reserved, (max(held) + 1) * grp.page_size if held else 0)
 
     def release(self, request_id) -> None:
         """The request ended (or is preempted): give everything back."""

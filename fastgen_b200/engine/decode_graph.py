@@ -48,6 +48,7 @@ class _Bucket:
         self.dev[2 * size : 3 * size] = -1  # until a step fills them, all lanes are padding
         self.dev[3 * size : 4 * size] = torch.arange(size, dtype=torch.int32, device=device)
         self.dev[4 * size :] = 1
+        self.seq_start = torch.arange(size + 1, dtype=torch.int32, device=device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.n_kernels = 0
@@ -57,7 +58,8 @@ class _Bucket:
         ctx = StepContext(device)
         ctx.tokens, ctx.pos, ctx.req = self.dev[:n], self.dev[n : 2 * n], self.dev[2 * n : 3 * n]
         ctx.want_rows = self.dev[3 * n : 4 * n]
-        ctx.seq_slot = ctx.req
+        # every sequence is its one token: slot and cached tokens are the token's slot and position
+        ctx.seq_slot, ctx.seq_start, ctx.seq_cached = ctx.req, self.seq_start, ctx.pos
         ctx.n_tokens = ctx.n_seqs = ctx.n_want = n
         # every sequence is one token: one-token tiles for kernels that tile all
         # sequences, none for kernels that only take longer ones

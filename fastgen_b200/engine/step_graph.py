@@ -61,7 +61,8 @@ class _Shape:
         self.size = 0  # ints of the buffer in use
         self.off = {}
         for name, n in (("tokens", n_tokens), ("pos", n_tokens), ("req", n_tokens), ("want", n_want),
-                        ("single_req", n_singles), ("single_tok", n_singles)):
+                        ("single_req", n_singles), ("single_tok", n_singles),
+                        ("seq_slot", max_seqs), ("seq_start", max_seqs + 1), ("seq_cached", max_seqs)):
             self.off[name] = self.size
             self.size += n
         self.capacity = self.size + 3 * 4 * (n_tokens + max_seqs + 8) + 4  # room for four tile lists
@@ -100,6 +101,10 @@ class _Shape:
         ctx.tokens, ctx.pos, ctx.req = self.view("tokens", t), self.view("pos", t), self.view("req", t)
         ctx.want_rows = self.view("want", self.n_want)
         ctx.n_tokens, ctx.n_seqs, ctx.n_want = t, self.max_seqs, self.n_want
+        # per sequence, for mixers with a state: padding sequences have slot -1 and no tokens
+        ctx.seq_slot = self.view("seq_slot", self.max_seqs)
+        ctx.seq_start = self.view("seq_start", self.max_seqs + 1)
+        ctx.seq_cached = self.view("seq_cached", self.max_seqs)
         ctx.attention_tiles = self.tiles_for
         if self.n_singles:
             singles = SingleTokens(self.view("single_req", self.n_singles), self.view("single_tok", self.n_singles),
@@ -166,6 +171,13 @@ class StepGraphs:
         host[o["req"] + n : o["req"] + sh.n_tokens] = -1  # padding tokens belong to no request
         host[o["want"] : o["want"] + len(want)] = want
         host[o["want"] + len(want) : o["want"] + sh.n_want] = 0
+        b = len(ctx_host.host_seq_slot)
+        host[o["seq_slot"] : o["seq_slot"] + b] = ctx_host.host_seq_slot
+        host[o["seq_slot"] + b : o["seq_slot"] + sh.max_seqs] = -1
+        host[o["seq_start"] : o["seq_start"] + b + 1] = ctx_host.host_seq_start
+        host[o["seq_start"] + b + 1 : o["seq_start"] + sh.max_seqs + 1] = n
+        host[o["seq_cached"] : o["seq_cached"] + b] = ctx_host.host_seq_cached
+        host[o["seq_cached"] + b : o["seq_cached"] + sh.max_seqs] = 0
         if sh.n_singles:
             s_req, s_tok = [], []
             for b, slot_b in enumerate(ctx_host.host_seq_slot):
@@ -205,6 +217,7 @@ class StepGraphs:
         sh.dev[sh.off["req"] : sh.off["req"] + sh.n_tokens] = -1  # every token is padding while capturing
         if sh.n_singles:
             sh.dev[sh.off["single_req"] : sh.off["single_req"] + sh.n_singles] = -1
+        sh.dev[sh.off["seq_slot"] : sh.off["seq_slot"] + sh.max_seqs] = -1
         ctx = sh.context()
         model.forward(ctx, memories)  # eagerly once: libraries choose their kernels, the tile lists get their places
         sh.graph, sh.logits, sh.n_kernels = self.decode_graphs.capture(lambda: model.forward(ctx, memories))

@@ -30,7 +30,7 @@ class LatentAttention(Mixer):
     """
 
     params: LatentAttentionParams
-    graph_safe = False
+    graph_safe = True
 
     def __init__(self, spec) -> None:
         super().__init__(spec)
