@@ -199,7 +199,7 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
                                          int table_width, int page_size, int n_pages, const int* pos,
                                          const int* tile_req, const int* tile_tok0, const int* tile_ntok,
                                          int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
-                                         float scale, int* status, cudaStream_t stream) {
+                                         int keep_first, float scale, int* status, cudaStream_t stream) {
   using namespace fg_mma;
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_bf16: library built for head size %d, got %d",
@@ -222,7 +222,8 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
   kern<<<grid, THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-      tile_ntok, n_kv_heads, group, hpb, window, scale * 1.4426950408889634f, status, nullptr, nullptr, nullptr);
+      tile_ntok, n_kv_heads, group, hpb, window, scale * 1.4426950408889634f, status, nullptr, nullptr, nullptr,
+      window > 0 ? keep_first : 0);
   FG_CHECK_LAUNCH("fg_attention_prefill_bf16");
   return 0;
 }
@@ -259,7 +260,7 @@ extern "C" int fg_attention_sigmoid_prefill_bf16(const void* q, int q_stride, vo
   kern<<<grid, THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-      tile_ntok, n_kv_heads, group, hpb, window, scale, status, gate, r1, r2);
+      tile_ntok, n_kv_heads, group, hpb, window, scale, status, gate, r1, r2, 0);
   FG_CHECK_LAUNCH("fg_attention_sigmoid_prefill_bf16");
   return 0;
 }
@@ -270,9 +271,9 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         const void* k_pages, const void* v_pages, const int* block_table,
                                         int table_width, int page_size, int n_pages, const int* pos,
                                         const int* seq_req, const int* seq_tok, int n_seqs, int n_heads,
-                                        int n_kv_heads, int head_dim, int window, float scale, float* scratch,
-                                        long long scratch_floats, int max_splits, const float* out_freqs,
-                                        int* status, cudaStream_t stream) {
+                                        int n_kv_heads, int head_dim, int window, int keep_first, float scale,
+                                        float* scratch, long long scratch_floats, int max_splits,
+                                        const float* out_freqs, int* status, cudaStream_t stream) {
   using namespace fg_mma;
   if (n_seqs == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_bf16: library built for head size %d, got %d",
@@ -301,12 +302,12 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
   kern<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
                                         (const __nv_bfloat16*)v_pages, block_table, table_width, page_size,
                                         n_pages, pos, seq_req, seq_tok, n_heads, n_kv_heads, group, window,
-                                        scale_log2, scratch, max_splits, status);
+                                        scale_log2, scratch, max_splits, status, keep_first);
   FG_CHECK_LAUNCH("fg_attention_decode_bf16");
   dim3 cgrid(n_heads, n_seqs);
   attention_combine_kernel<FG_HEAD_DIM><<<cgrid, COMBINE_THREADS, 0, stream>>>(
       scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, nullptr, status,
-      out_freqs);
+      out_freqs, keep_first);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }
@@ -389,7 +390,7 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
   dim3 cgrid(n_heads, n_seqs);
   fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(fg_mma::COMBINE_THREADS), 0, stream,
                 (const float*)partials, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window,
-                max_splits, combine_pairs, status, out_freqs);
+                max_splits, combine_pairs, status, out_freqs, 0);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }

@@ -82,11 +82,13 @@ template <int HD>
 __device__ __forceinline__ void kv_row_offsets(long long* row_off, const int* __restrict__ table_row,
                                                int table_width, int page_size, int n_pages, int n_kv_heads,
                                                int g, int k0, int rows, int k_begin, int k_end, int tid,
-                                               int* status) {
+                                               int* status, int keep_first = 0) {
+  // rows for the positions [k_begin, k_end) and for the first keep_first positions (those a
+  // window keeps visible); the others get no offset and are zero-filled
   if (tid < rows) {
     const int j = k0 + tid;
     long long off = -1;
-    if (j >= k_begin && j < k_end) {
+    if ((j >= k_begin || j < keep_first) && j < k_end) {
       const int logical = j / page_size;
       const int page = logical < table_width ? table_row[logical] : -1;
       if (page >= 0 && page < n_pages)
@@ -220,7 +222,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
                          const int* __restrict__ tile_ntok, int n_kv_heads, int group, int heads_per_block,
                          int window, float scale_log2, int* status, const float* __restrict__ gate,
-                         const float* __restrict__ dist_r1, const float* __restrict__ dist_r2) {
+                         const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, int keep_first) {
+  // keep_first (with a window): so many of the sequence's first positions stay visible to every
+  // query; the key tiles that hold them are walked before the tiles of the window
   constexpr int LD = Tile<HD>::LD;
   constexpr int NT = PREFILL_KEYS / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -271,12 +275,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   const int k_begin = window > 0 ? max(0, min_pos - window + 1) : 0;
   const int k_end = max_pos + 1;
   const int* table_row = block_table + (size_t)b * table_width;
-  const int n_tiles = (k_end - k_lo + PREFILL_KEYS - 1) / PREFILL_KEYS;
+  // tiles of kept first positions that lie wholly before the window's first tile
+  const int n_keep = (window > 0 && keep_first > 0)
+                         ? min(k_lo, (keep_first + PREFILL_KEYS - 1) / PREFILL_KEYS * PREFILL_KEYS) / PREFILL_KEYS
+                         : 0;
+  const int n_tiles = n_keep + (k_end - k_lo + PREFILL_KEYS - 1) / PREFILL_KEYS;
+  auto tile_k0 = [&](int t) { return t < n_keep ? t * PREFILL_KEYS : k_lo + (t - n_keep) * PREFILL_KEYS; };
 
   // offsets of tile t's rows are computed one tile ahead of its copies
   auto offsets = [&](int t) {
     kv_row_offsets<HD>(row_off[t & 1], table_row, table_width, page_size, n_pages, n_kv_heads, g,
-                       k_lo + t * PREFILL_KEYS, PREFILL_KEYS, k_begin, k_end, tid, status);
+                       tile_k0(t), PREFILL_KEYS, k_begin, k_end, tid, status, window > 0 ? keep_first : 0);
   };
   auto issue = [&](int t) {
     const int stage = t & 1;
@@ -328,7 +337,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     __syncthreads();
     // tile t's rows have landed and its offsets are no longer needed
     if (t + 2 < n_tiles) offsets(t + 2);
-    const int k0 = k_lo + t * PREFILL_KEYS;
+    const int k0 = tile_k0(t);
     if (k0 <= warp_max) {
       const __nv_bfloat16* ks = Ks + (t & 1) * PREFILL_KEYS * LD;
       const __nv_bfloat16* vs = Vs + (t & 1) * PREFILL_KEYS * LD;
@@ -342,7 +351,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         for (int e = 0; e < 4; ++e) {
           const int j = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
           const int p = (e < 2) ? p0 : p1;
-          const bool vis = p >= 0 && j <= p && (window <= 0 || j > p - window);
+          const bool vis = p >= 0 && j <= p && (window <= 0 || j > p - window || j < keep_first);
           if (SIGMOID) {
             float wgt;
             {
@@ -460,7 +469,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const int* __restrict__ pos, const int* __restrict__ seq_req,
                         const int* __restrict__ seq_tok, int n_heads, int n_kv_heads, int group,
                         int window, float scale_log2, float* __restrict__ scratch, int max_splits,
-                        int* status) {
+                        int* status, int keep_first) {
   static_assert(THREADS >= DECODE_SPLIT, "one thread per key position computes its row offset");
   constexpr int LD = Tile<HD>::LD;
   constexpr int NT = 4;  // 32 key positions per warp
@@ -478,12 +487,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   const int k0 = split * DECODE_SPLIT;
   if (k0 > p) return;  // this split lies beyond the request's keys
   const int k_begin = window > 0 ? max(0, p - window + 1) : 0;
-  if (k0 + DECODE_SPLIT <= k_begin) return;  // wholly before the window
+  if (window <= 0) keep_first = 0;
+  if (k0 + DECODE_SPLIT <= k_begin && k0 >= keep_first) return;  // wholly before the window, nothing kept
   const int k_end = p + 1;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   kv_row_offsets<HD>(row_off, block_table + (size_t)b * table_width, table_width, page_size, n_pages,
-                     n_kv_heads, g, k0, DECODE_SPLIT, k_begin, k_end, tid, status);
+                     n_kv_heads, g, k0, DECODE_SPLIT, k_begin, k_end, tid, status, keep_first);
   __syncthreads();
   load_kv_rows<HD>(Ks, k_pages, row_off, DECODE_SPLIT, tid, THREADS);
   cp_async_commit();
@@ -520,7 +530,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int j = k0 + warp * 32 + nt * 8 + 2 * (lane & 3) + (e & 1);
-        const bool vis = j >= k_begin && j < k_end;
+        const bool vis = (j >= k_begin || j < keep_first) && j < k_end;
         s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
       }
     float o[HD / 8][4];
@@ -598,7 +608,10 @@ __global__ void __launch_bounds__(COMBINE_THREADS)
 attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, int out_stride,
                          const int* __restrict__ pos, const int* __restrict__ seq_req,
                          const int* __restrict__ seq_tok, int n_heads, int window, int max_splits,
-                         const int* first_pair, int* status, const float* __restrict__ out_freqs) {
+                         const int* first_pair, int* status, const float* __restrict__ out_freqs,
+                         int keep_first) {
+  // keep_first (with a window, partials numbered [request][head][split] only): the splits that
+  // hold kept first positions are summed before those of the window
   // out_freqs: null, or HD/2 frequencies by which the output's adjacent pairs are turned
   // (angle position * frequency) before they are stored: a model that caches values turned by
   // their positions turns the sum back here, with the negated table.
@@ -637,9 +650,14 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   const float* base = first_pair != nullptr
                           ? scratch + ((size_t)(first_pair[seq] - s_lo) * n_heads + head) * PS
                           : scratch + ((size_t)seq * n_heads + head) * max_splits * PS;
+  const int n_keep = (window > 0 && keep_first > 0 && first_pair == nullptr)
+                         ? min(s_lo, (keep_first + DECODE_SPLIT - 1) / DECODE_SPLIT)
+                         : 0;
+  const int n_parts = n_keep + (s_hi - s_lo + 1);
+  auto split_of = [&](int i) { return i < n_keep ? i : s_lo + (i - n_keep); };
   // the overall maximum
   float mm = -INFINITY;
-  for (int s = s_lo + tid; s <= s_hi; s += COMBINE_THREADS) mm = fmaxf(mm, base[(size_t)s * step + HD]);
+  for (int i = tid; i < n_parts; i += COMBINE_THREADS) mm = fmaxf(mm, base[(size_t)split_of(i) * step + HD]);
   mm = warp_max(mm);
   if (lane == 0) red[warp] = mm;
   __syncthreads();
@@ -652,8 +670,8 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   for (int i = 0; i < NV; ++i) acc[i] = make_float2(0.f, 0.f);
   float ll = 0.f;
 #pragma unroll 4
-  for (int s = s_lo + warp; s <= s_hi; s += WARPS) {
-    const float* part = base + (size_t)s * step;
+  for (int i = warp; i < n_parts; i += WARPS) {
+    const float* part = base + (size_t)split_of(i) * step;
     const float ms = part[HD];
     const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
     ll += wgt * part[HD + 1];

@@ -200,6 +200,19 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     )
 
 
+def latent_library(rank: int, rot_dim: int) -> ctypes.CDLL:
+    """The tensor-core kernels of the attention over a cached latent, compiled per latent size."""
+    return load(f"fg_latent_r{rank}_t{rot_dim}", ["latent_mma.cu", "errors.cu"],
+                [f"FG_LATENT_RANK={rank}", f"FG_LATENT_ROT={rot_dim}"])
+
+
+def latent_mma_supported(rank: int, rot_dim: int) -> bool:
+    """Whether ``latent_mma.cu`` takes a latent of these sizes (the others run on the CUDA cores)."""
+    r16 = -(-rank // 16) * 16
+    return rank % 8 == 0 and rot_dim % 2 == 0 and 8 <= rank <= 512 and (r16 <= 256 or r16 % 32 == 0) \
+        and -(-(rank + rot_dim) // 16) * 16 <= 640
+
+
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> None:
     """Compile every library (used by the build check and before shipping)."""
     _compile("fg_core", CORE_SOURCES)

@@ -81,8 +81,9 @@ _ATTN_SIGNATURES = {
                                          _P, _P, _P, _P, ctypes.c_longlong, _I, _P, _P],
     "fg_attention_sigmoid_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                           _F, _P, _P, _P, _P, _P],
-    "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
-    "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
+    "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
+                                  _P],
+    "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
                                  ctypes.c_longlong, _I, _P, _P, _P],
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P],
@@ -153,6 +154,25 @@ def _check(lib: ctypes.CDLL, rc: int) -> None:
 
 _core = None
 _attn = {}
+_latent = {}
+
+_LATENT_SIGNATURES = {
+    "fg_latent_attention_mma": [_P, _L, _L, _P, _L, _L, _P, _L, _L, _P, _L, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I,
+                                _I, _I, _I, _F, _I, _I, _P, ctypes.c_longlong, _P, _P],
+}
+
+
+def latent(rank: int, rot_dim: int):
+    """The tensor-core library of the attention over a cached latent of these sizes."""
+    key = (rank, rot_dim)
+    lib = _latent.get(key)
+    if lib is None:
+        lib = build.latent_library(rank, rot_dim)
+        _declare(lib, _LATENT_SIGNATURES)
+        lib.fg_latent_mma_scratch_floats.argtypes = [_I, _I, _I]
+        lib.fg_latent_mma_scratch_floats.restype = ctypes.c_longlong
+        _latent[key] = lib
+    return lib
 
 
 def core():
@@ -422,6 +442,31 @@ class Ops:
         pages = memory.k_pages
         assert qa.stride(2) == 1 and qt.stride(2) == 1 and out.stride(2) == 1 and pages.is_contiguous()
         assert gate is None or gate.stride(1) == 1
+        even = all(v % 2 == 0 for v in (*qa.stride()[:2], *qt.stride()[:2], *out.stride()[:2], qt.storage_offset()))
+        if (qa.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and even
+                and build.latent_mma_supported(rank, rot_dim) and pages.shape[-1] == -(-(rank + rot_dim) // 8) * 8):
+            # bfloat16: the tensor cores; few tiles (single tokens) are cut into stretches of keys
+            lib = latent(rank, rot_dim)
+            rows, keys = lib.fg_latent_mma_rows(), lib.fg_latent_mma_keys()
+            tiles = ctx.attention_tiles(attention_tiling(n_heads, 1, rows), 1)
+            max_keys = tiles.max_keys or memory.block_table.shape[1] * memory.page_size
+            blocks = tiles.n * -(-n_heads // min(n_heads, rows))
+            n_splits = 1
+            if blocks < 96:
+                n_splits = max(1, min(-(-max_keys // (4 * keys)), -(-296 // blocks), 32))
+            per = -(-(-(-max_keys // n_splits)) // keys) * keys
+            n_splits = -(-max_keys // per)
+            floats = lib.fg_latent_mma_scratch_floats(tiles.n, n_heads, n_splits)
+            scratch = self._decode_scratch(floats) if floats else None
+            _check(lib, lib.fg_latent_attention_mma(
+                _ptr(qa), qa.stride(1), qa.stride(0), _ptr(qt), qt.stride(0), qt.stride(1), _ptr(out), out.stride(1),
+                out.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(pages),
+                _ptr(memory.block_table), memory.block_table.shape[1], memory.page_size, pages.shape[0], _ptr(ctx.pos),
+                _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n, n_heads, rank, rot_dim, pages.shape[-1],
+                float(scale), n_splits, per, _ptr(scratch), scratch.numel() if scratch is not None else 0,
+                _ptr(self.status), _stream()))
+            Ops.launches += int(n_splits > 1)  # the merge of the stretches
+            return out
         tiles = ctx.attention_tiles(attention_tiling(n_heads, 1, SIMT_ROWS), 1)
         _check(self.lib, self.lib.fg_latent_attention_simt(
             _ptr(qa), _code(qa.dtype), qa.stride(1), qa.stride(0), _ptr(qt), qt.stride(0), qt.stride(1), _ptr(out),
@@ -690,8 +735,7 @@ class Ops:
         common = (_ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
                   k_pages.shape[0], _ptr(ctx.pos))
         keep_first = int(keep_first) if window else 0
-        if q.dtype == torch.float32 or keep_first:
-            # float32, and windows that keep a sequence's first positions visible: the CUDA-core kernel
+        if q.dtype == torch.float32:
             tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, SIMT_ROWS), 1)
             _check(lib, lib.fg_attention_simt(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), *common,
@@ -699,7 +743,9 @@ class Ops:
                 n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale),
                 _ptr(self.status), _stream()))
             return False
-        use_tma = memory.tensor_maps is not None
+        # windows that keep a sequence's first positions visible run on the mma.sync kernels, which
+        # walk the tiles of the kept positions before those of the window
+        use_tma = memory.tensor_maps is not None and not keep_first
         rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
         tiling = attention_tiling(n_heads, n_kv_heads, rows)
         tiles = ctx.attention_tiles(tiling, 2)
@@ -725,7 +771,7 @@ class Ops:
             _check(lib, lib.fg_attention_prefill_bf16(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
-                n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
+                n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale),
                 _ptr(self.status), _stream()))
         singles = ctx.single_tokens()
         fused = out_freqs is not None and tiles.n == 0 and singles.n > 0
@@ -742,6 +788,8 @@ class Ops:
             scratch = self._decode_scratch(floats)
             head = (_ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
                     int(window or 0), float(scale), _ptr(scratch), scratch.numel(), max_splits)
+            if not tma:
+                head = head[:7] + (keep_first,) + head[7:]
             if tma:
                 _check(lib, lib.fg_attention_decode_tma_bf16(
                     _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,

@@ -1,7 +1,7 @@
 """Throughput of one design beside another at equal size, step by step and kernel by kernel.
 
-``bench.py --design sinorax`` runs this: prefill and decode throughput of a Sinorax model at a
-few sizes that resemble a real model's layers (random weights), beside a Llama-shaped model of
+``bench.py --design sinorax|zeladra`` runs this: prefill and decode throughput of a model of that
+design at a few sizes that resemble a real model's layers (random weights), beside a Llama-shaped model of
 the same width, heads, head size, number of layers and number of parameters a layer, and the
 time of each kernel family of the two designs at those sizes with its fraction of the roofline
 (HBM bandwidth for the elementwise kernels and single-token attention, tensor throughput for
@@ -55,6 +55,30 @@ def sinorax_config(width, layers, heads, kv, head_dim, ffn, vocab, window, kinds
                 embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)), layers=out)
 
 
+def zeladra_config(width, layers, heads, kv, head_dim, ffn, vocab, window) -> dict:
+    """Latent attention, the state-space mixer and windowed attention that keeps the first four
+    positions, in turn (every second latent layer reads the first one's cache), on two residual
+    streams; every layer has the gated feed-forward of the Llama shape."""
+    latent = dict(heads=heads, dim=head_dim, rot_dim=head_dim // 2, vdim=head_dim, q_rank=width * 3 // 4,
+                  kv_rank=4 * head_dim, scale=(head_dim * 3 // 2) ** -0.5,
+                  rot=dict(dims=head_dim // 2, base=500000.0, scaling=dict(factor=4.0, original=8192, fast=32.0, slow=1.0)))
+    ssm = dict(heads=2 * width // 64, vdim=64, state=128, groups=8, conv=4, norm_groups=8)
+    att = dict(heads=heads, kv_heads=kv, dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5,
+               rot=dict(dims=head_dim, base=500000.0), mask=dict(size=window, keep_first=4))
+    out, first_latent = [], None
+    for i in range(layers):
+        kind = ("latent_attention", "mamba2", "attention")[i % 3]
+        mixer = dict({"latent_attention": latent, "mamba2": ssm, "attention": att}[kind])
+        if kind == "latent_attention":
+            if first_latent is None:
+                first_latent = i
+            elif (i // 3) % 2 == 1:
+                mixer["kv_from"] = first_latent
+        out.append(dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=ffn)))
+    return dict(architecture="Zeladra", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
+                streams=2, layers=out)
+
+
 class Timer:
     """CUDA-event times of single launches, each after a write larger than L2."""
 
@@ -91,7 +115,8 @@ def _engine(cfg, device, max_requests, tokens):
 def _fill(engine) -> None:
     for grp in engine.cache.groups:
         grp.k_pages.normal_(0.0, 1.0)
-        grp.v_pages.normal_(0.0, 1.0)
+        if grp.v_pages is not None:
+            grp.v_pages.normal_(0.0, 1.0)
 
 
 def model_throughput(cfg, device) -> Dict[str, float]:
@@ -275,9 +300,150 @@ def kernel_table(size, device, peaks) -> Dict[str, dict]:
     return table
 
 
-def run(sizes: List[str], peaks: dict, kernels: bool = True) -> dict:
+def _mixer_times(cfg, device, timer: Timer, layer: int) -> Dict[str, float]:
+    """A whole mixer of one layer alone (its projections included): a 2,048-token prompt, and 8
+    single tokens at position 2,048."""
+    from ..engine import StepEntry
+
+    engine = _engine(cfg, device, DECODE_BATCH, DECODE_CONTEXT)
+    _fill(engine)
+    mixer = engine.model.blocks[layer].mixer
+    memory = engine.memories[layer]
+    width = engine.model.args.dim
+    gen = torch.Generator().manual_seed(SEED)
+    out = {}
+
+    def context(entries):
+        reqs = engine._validate(entries)
+        for e, r in zip(entries, reqs):
+            engine.cache.reserve(r, r.length + len(e.tokens))
+        engine.cache.flush_tables()
+        return engine.build_context(entries, reqs)
+
+    engine.admit("p")
+    ctx = context([StepEntry("p", [1] * PREFILL_TOKENS, [])])
+    x = torch.randn(PREFILL_TOKENS, width, generator=gen).to(device, torch.bfloat16)
+    out["prefill_us"] = round(timer.us(lambda: mixer.forward(x, ctx, memory)), 1)
+    engine.release("p")
+    ids = [f"d{i}" for i in range(DECODE_BATCH)]
+    for rid in ids:
+        r = engine.admit(rid)
+        engine.cache.reserve(r, DECODE_CONTEXT - 1)
+        engine.cache.advance(r, DECODE_CONTEXT - 1)
+    ctx = context([StepEntry(rid, [1], []) for rid in ids])
+    x = torch.randn(DECODE_BATCH, width, generator=gen).to(device, torch.bfloat16)
+    out["decode_us"] = round(timer.us(lambda: mixer.forward(x, ctx, memory)), 1)
+    engine.ops.check_status()
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def zeladra_kernel_table(size, device, peaks) -> Dict[str, dict]:
+    """The kernels of the Zeladra design alone at one size, each beside the like kernel of the
+    Llama shape where there is one: microseconds and the fraction of the roofline."""
+    from ..cache import LayerMemory
+    from ..csrc.ops import Ops
+    from ..engine.step import StepContext
+    from ..parts.base import StreamUpdate
+
+    width, _layers, heads, kv, head_dim, ffn, vocab, window = size
+    ops = Ops(torch.bfloat16, device)
+    timer = Timer(device)
+    gen = torch.Generator().manual_seed(SEED)
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    table: Dict[str, dict] = {}
+
+    def bw(name, us, nbytes):
+        table[name] = dict(us=round(us, 1), gbs=round(nbytes / (us * 1e-6) / 1e9, 1), hbm_frac=round(nbytes / (us * 1e-6) / hbm, 3))
+
+    def rand(*shape, dtype=torch.bfloat16):
+        return torch.randn(*shape, generator=gen).to(device, dtype)
+
+    streams = 2
+    for t in (PREFILL_TOKENS, DECODE_BATCH):
+        h, delta = rand(t, streams, width, dtype=torch.float32), rand(t, width)
+        out = torch.empty(t, width, dtype=torch.bfloat16, device=device)
+        w, b = rand(width, dtype=torch.float32), rand(width, dtype=torch.float32)
+        mix, oc, ic = (rand(*sh, dtype=torch.float32) for sh in ((streams, streams), (streams,), (streams,)))
+        up = StreamUpdate(delta, mix, oc)
+        bw(f"norm+sum t={t}: layer norm over {streams} streams (update, sum, norm)",
+           timer.us(lambda: ops.stream_norm(h, w, b, 1e-5, out, update=up, in_coef=ic)), t * width * (8 * streams + 2 + 2))
+        h1, wb = rand(t, width, dtype=torch.float32), rand(width)
+        bw(f"norm+sum t={t}: rmsnorm (sum, norm)", timer.us(lambda: ops.rmsnorm(h1, wb, 1e-5, out=out, delta=delta)),
+           t * width * (4 + 4 + 2 + 2))
+
+    # the state-space mixer's own kernels at this size
+    ssm = zeladra_config(*size)["layers"][1]["mixer"]
+    H, P, N, G, taps = ssm["heads"], ssm["vdim"], ssm["state"], ssm["groups"], ssm["conv"]
+    inner, channels = H * P, H * P + 2 * G * N
+    cols = 2 * inner + 2 * G * N + H
+    state = torch.zeros(DECODE_BATCH, H * N * P + (taps - 1) * channels, dtype=torch.float32, device=device)
+    conv_w, conv_b = rand(channels, taps, dtype=torch.float32), rand(channels, dtype=torch.float32)
+    vec = [rand(H, dtype=torch.float32) for _ in range(3)]
+    norm_w = rand(inner, dtype=torch.float32)
+    for t, n_seqs in ((PREFILL_TOKENS, 1), (DECODE_BATCH, DECODE_BATCH)):
+        proj = rand(t, cols)
+        ctx = StepContext(device)
+        per = t // n_seqs
+        ctx.req = torch.arange(n_seqs, dtype=torch.int32, device=device).repeat_interleave(per)
+        ctx.seq_slot = torch.arange(n_seqs, dtype=torch.int32, device=device)
+        ctx.seq_start = torch.arange(0, t + 1, per, dtype=torch.int32, device=device)
+        ctx.n_tokens, ctx.n_seqs = t, n_seqs
+        xbc = ops.mamba2_conv(proj, inner, channels, conv_w, conv_b, state, H * N * P, taps, ctx)
+        bw(f"state-space t={t}: convolution + SiLU", timer.us(lambda: ops.mamba2_conv(
+            proj, inner, channels, conv_w, conv_b, state, H * N * P, taps, ctx)), t * channels * (2 + 4))
+        y = ops.mamba2_scan(xbc, proj, inner + channels, *vec, state, ctx, H, G, N, P)
+        state_bytes = n_seqs * H * N * P * 8
+        bw(f"state-space t={t}: recurrence ({n_seqs} sequences)", timer.us(lambda: ops.mamba2_scan(
+            xbc, proj, inner + channels, *vec, state, ctx, H, G, N, P)), t * (channels + inner) * 4 + state_bytes)
+        bw(f"state-space t={t}: gate + norm in parts", timer.us(lambda: ops.gated_part_norm(
+            y, proj[:, :inner], norm_w, ssm["norm_groups"], 1e-5, ctx)), t * inner * (4 + 2 + 2))
+        state.zero_()
+
+    geometry = (heads, kv, head_dim)
+    small = (width, 3, heads, kv, head_dim, ffn, 1024)
+    z = zeladra_config(*small, window)
+    lat = z["layers"][0]["mixer"]
+    table[f"attention softmax (zeladra 'attention', window {window}, keeps 4)"] = _attention_times(z, device, timer, 2, window, *geometry)
+    table[f"attention softmax (llama, window {window})"] = _attention_times(llama_config(*small, window=window), device, timer, 0,
+                                                                          window, *geometry)
+    for name, row in table.items():
+        if "prefill_tflops" in row:
+            row["prefill_tensor_frac"] = round(row["prefill_tflops"] * 1e12 / tensor, 3)
+            row["decode_hbm_frac"] = round(row["decode_gbs"] * 1e9 / hbm, 3)
+    # whole mixers (projections included)
+    row = _mixer_times(z, device, timer, 0)
+    keys = PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2
+    entry = lat["kv_rank"] + lat["rot_dim"]
+    row["attention_flops_prefill"] = 2 * heads * keys * (entry + lat["kv_rank"])
+    row["cache_bytes_decode"] = DECODE_BATCH * DECODE_CONTEXT * entry * 2
+    table["mixer latent attention (zeladra, causal; whole mixer)"] = row
+    table["mixer state-space (zeladra; whole mixer)"] = _mixer_times(z, device, timer, 1)
+    table["mixer attention (zeladra, window; whole mixer)"] = _mixer_times(z, device, timer, 2)
+    table["mixer attention (llama, causal; whole mixer)"] = _mixer_times(llama_config(*small), device, timer, 0)
+    return table
+
+
+def run(sizes: List[str], peaks: dict, kernels: bool = True, design: str = "sinorax") -> dict:
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
+    if design == "zeladra":
+        out = {"metric": "prefill and decode tokens/s of Zeladra beside a Llama-shaped model of equal size (bf16, random weights)",
+               "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+               "config": dict(prefill_tokens=PREFILL_TOKENS, decode_batch=DECODE_BATCH, decode_context=DECODE_CONTEXT, page=PAGE,
+                              l2="flushed before every timed kernel; model steps stream all weights"),
+               "peaks": peaks, "sizes": {}}
+        for name in sizes:
+            size = SIZES[name]
+            entry = dict(width=size[0], layers=size[1], heads=size[2], kv_heads=size[3], head_dim=size[4], swiglu_ffn=size[5],
+                         vocab=size[6], window=size[7])
+            entry["zeladra"] = model_throughput(zeladra_config(*size), device)
+            entry["llama"] = model_throughput(llama_config(*size[:7]), device)
+            if kernels:
+                entry["kernels"] = zeladra_kernel_table(size, device, peaks)
+            out["sizes"][name] = entry
+        return out
     out = {"metric": "prefill and decode tokens/s of Sinorax beside a Llama-shaped model of equal size (bf16, random weights)",
            "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
            "config": dict(prefill_tokens=PREFILL_TOKENS, decode_batch=DECODE_BATCH, decode_context=DECODE_CONTEXT, page=PAGE,
