@@ -23,9 +23,12 @@
 // out[t, c] = silu(bias[c] + sum_k w[c, k] * in[t - (taps-1-k), c]); inputs before the step's
 // first token of the sequence come from the state.
 constexpr int CONV_THREADS = 128;
-constexpr int CONV_TOKENS = 8;
+constexpr int CONV_TOKENS = 32;
 constexpr int CONV_MAX_TAPS = 8;
 
+// A thread walks one channel over the block's tokens and keeps the last taps-1 inputs in
+// registers; they are fetched anew (from the step's tokens or from the state) only where a
+// sequence's part of the step begins or the block's stretch of tokens does.
 template <typename T>
 __global__ void __launch_bounds__(CONV_THREADS)
 conv_silu_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ out, long out_stride,
@@ -39,25 +42,47 @@ conv_silu_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ o
   for (int k = 0; k < CONV_MAX_TAPS; ++k) wk[k] = k < taps ? w[(size_t)c * taps + k] : 0.f;
   const float bc = bias ? bias[c] : 0.f;
   const int t0 = blockIdx.x * CONV_TOKENS;
+  float hist[CONV_MAX_TAPS];  // hist[j]: the input j + 1 tokens ago
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) hist[j] = 0.f;
+  int prev_slot = -1;
   for (int t = t0; t < min(t0 + CONV_TOKENS, n_tokens); ++t) {
     const int slot = req[t];
-    if (slot < 0) continue;
-    // how many of the taps-1 tokens before t the step itself brings
-    int have = 0;
-    while (have < taps - 1 && t - have - 1 >= 0 && req[t - have - 1] == slot) ++have;
-    const float* st = state + (size_t)slot * state_stride + conv_offset;
+    if (slot < 0) {
+      prev_slot = -1;
+      continue;
+    }
+    if (slot != prev_slot) {
+      // how many of the taps-1 tokens before t the step itself brings
+      int have = 0;
+      while (have < taps - 1 && t - have - 1 >= 0 && req[t - have - 1] == slot) ++have;
+      const float* st = state + (size_t)slot * state_stride + conv_offset;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+        const int back = j + 1;
+        if (back < taps)
+          hist[j] = back <= have ? to_f32<T>(in[(size_t)(t - back) * in_stride + c])
+                                 : st[(size_t)(taps - 1 + have - back) * channels + c];
+      }
+      prev_slot = slot;
+    }
+    const float cur = to_f32<T>(in[(size_t)t * in_stride + c]);
     float acc = bc;
 #pragma unroll
     for (int k = 0; k < CONV_MAX_TAPS; ++k) {
       if (k < taps) {
         const int back = taps - 1 - k;  // this tap meets the input `back` tokens ago
-        float v;
-        if (back <= have) v = to_f32<T>(in[(size_t)(t - back) * in_stride + c]);
-        else v = st[(size_t)(taps - 1 + have - back) * channels + c];
+        float v = cur;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+          if (back == j + 1) v = hist[j];
         acc = fmaf(wk[k], v, acc);
       }
     }
     out[(size_t)t * out_stride + c] = acc / (1.f + expf(-acc));
+#pragma unroll
+    for (int j = CONV_MAX_TAPS - 1; j > 0; --j) hist[j] = hist[j - 1];
+    hist[0] = cur;
   }
 }
 
@@ -83,11 +108,17 @@ conv_state_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ 
 // ---- the recurrence ---------------------------------------------------------------------------
 // A block works on (sequence, head, 16 columns of P); a thread on one column p and every
 // eighth row n of the state, which it keeps in registers.  Tokens are staged through shared
-// memory eight at a time.
+// memory sixteen at a time in two buffers: while a stage is computed, the next one's B, C and x
+// arrive by asynchronous copies and its raw step sizes wait in a register.
 constexpr int SCAN_PB = 16;      // columns of P a block
 constexpr int SCAN_LANES = 8;    // threads a column
 constexpr int SCAN_THREADS = SCAN_PB * SCAN_LANES;
-constexpr int SCAN_TOKENS = 8;   // tokens a stage
+constexpr int SCAN_TOKENS = 16;  // tokens a stage
+
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
 
 template <typename T, int NPT>
 __global__ void __launch_bounds__(SCAN_THREADS)
@@ -97,15 +128,17 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int heads, int groups,
                 int N, int P) {
   extern __shared__ float smem[];
-  float* Bs = smem;                        // [SCAN_TOKENS][N]
-  float* Cs = Bs + SCAN_TOKENS * N;        // [SCAN_TOKENS][N]
-  float* xs = Cs + SCAN_TOKENS * N;        // [SCAN_TOKENS][SCAN_PB]
-  float* dts = xs + SCAN_TOKENS * SCAN_PB;  // [SCAN_TOKENS]
-  float* decs = dts + SCAN_TOKENS;         // [SCAN_TOKENS]
+  const int stage_floats = 2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS;
+  auto Bs = [&](int buf) { return smem + buf * stage_floats; };               // [SCAN_TOKENS][N]
+  auto Cs = [&](int buf) { return Bs(buf) + SCAN_TOKENS * N; };               // [SCAN_TOKENS][N]
+  auto xs = [&](int buf) { return Cs(buf) + SCAN_TOKENS * N; };               // [SCAN_TOKENS][SCAN_PB]
+  auto dts = [&](int buf) { return xs(buf) + SCAN_TOKENS * SCAN_PB; };        // [SCAN_TOKENS]
+  auto decs = [&](int buf) { return dts(buf) + SCAN_TOKENS; };                // [SCAN_TOKENS]
 
   const int slot = seq_slot[blockIdx.x];
   if (slot < 0) return;
   const int start = seq_start[blockIdx.x], n_tok = seq_start[blockIdx.x + 1] - start;
+  if (n_tok <= 0) return;
   const int h = blockIdx.y, g = h / (heads / groups);
   const int p0 = blockIdx.z * SCAN_PB;
   const int tid = threadIdx.x;
@@ -125,43 +158,65 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
     s[i] = (p_ok && n < N) ? S[(size_t)n * P + p] : 0.f;
   }
 
-  for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
-    const int nt = min(SCAN_TOKENS, n_tok - t0);
-    __syncthreads();
+  const int n_stages = (n_tok + SCAN_TOKENS - 1) / SCAN_TOKENS;
+  auto issue = [&](int k) {
+    const int buf = k & 1, t0 = k * SCAN_TOKENS, nt = min(SCAN_TOKENS, n_tok - t0);
+    float *bs = Bs(buf), *cs = Cs(buf), *xx = xs(buf);
     for (int i = tid; i < nt * N; i += SCAN_THREADS) {
       const int tt = i / N, n = i - tt * N;
-      const float* row = xbc + (size_t)(start + t0 + tt) * xbc_stride;
-      Bs[tt * N + n] = row[inner + g * N + n];
-      Cs[tt * N + n] = row[inner + groups * N + g * N + n];
+      const float* row = xbc + (size_t)(start + t0 + tt) * xbc_stride + inner + g * N + n;
+      cp_async_4(bs + i, row);
+      cp_async_4(cs + i, row + groups * N);
     }
     for (int i = tid; i < nt * SCAN_PB; i += SCAN_THREADS) {
       const int tt = i / SCAN_PB, pp = i - tt * SCAN_PB;
-      xs[i] = p0 + pp < P ? xbc[(size_t)(start + t0 + tt) * xbc_stride + h * P + p0 + pp] : 0.f;
+      if (p0 + pp < P) cp_async_4(xx + i, xbc + (size_t)(start + t0 + tt) * xbc_stride + h * P + p0 + pp);
+      else xx[i] = 0.f;
     }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  auto raw_dt = [&](int k) {
+    const int t = k * SCAN_TOKENS + tid;
+    return (tid < SCAN_TOKENS && t < n_tok) ? to_f32<T>(dt_raw[(size_t)(start + t) * dt_stride + h]) : 0.f;
+  };
+  issue(0);
+  float dtr = raw_dt(0);
+
+  for (int k = 0; k < n_stages; ++k) {
+    const int buf = k & 1, t0 = k * SCAN_TOKENS, nt = min(SCAN_TOKENS, n_tok - t0);
     if (tid < nt) {
-      const float v = to_f32<T>(dt_raw[(size_t)(start + t0 + tid) * dt_stride + h]) + bias;
+      const float v = dtr + bias;
       const float dt = v > 20.f ? v : log1pf(expf(v));
-      dts[tid] = dt;
-      decs[tid] = expf(a * dt);
+      dts(buf)[tid] = dt;
+      decs(buf)[tid] = expf(a * dt);
+    }
+    if (k + 1 < n_stages) {
+      issue(k + 1);
+      dtr = raw_dt(k + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
+    const float *bs = Bs(buf), *cs = Cs(buf), *xx = xs(buf), *dd = dts(buf), *de = decs(buf);
     for (int tt = 0; tt < nt; ++tt) {
-      const float dt = dts[tt], dec = decs[tt];
-      const float xv = xs[tt * SCAN_PB + pl];
+      const float dt = dd[tt], dec = de[tt];
+      const float xv = xx[tt * SCAN_PB + pl];
       const float dx = dt * xv;
       float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < NPT; ++i) {
         const int n = lane + SCAN_LANES * i;
         if (n < N) {
-          s[i] = fmaf(dec, s[i], Bs[tt * N + n] * dx);
-          acc = fmaf(s[i], Cs[tt * N + n], acc);
+          s[i] = fmaf(dec, s[i], bs[tt * N + n] * dx);
+          acc = fmaf(s[i], cs[tt * N + n], acc);
         }
       }
 #pragma unroll
       for (int o = SCAN_LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (lane == 0 && p_ok) y[(size_t)(start + t0 + tt) * y_stride + h * P + p] = fmaf(dsk, xv, acc);
     }
+    __syncthreads();  // the stage is read to its end before the copies after next overwrite it
   }
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
@@ -240,7 +295,7 @@ static int launch_scan(const float* xbc, long xbc_stride, const T* dt_raw, long 
                        const int* seq_slot, const int* seq_start, int n_seqs, int heads, int groups, int N, int P,
                        cudaStream_t stream) {
   const dim3 grid(n_seqs, heads, (P + SCAN_PB - 1) / SCAN_PB);
-  const size_t smem = sizeof(float) * (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS);
+  const size_t smem = 2 * sizeof(float) * (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS);
   const int npt = (N + SCAN_LANES - 1) / SCAN_LANES;
 #define SCAN(NPT)                                                                                               \
   do {                                                                                                          \

@@ -18,7 +18,9 @@
 constexpr int SN_MAX_STREAMS = 8;
 constexpr int SN_THREADS = 256;
 
-template <typename TD, typename TO>
+// S is the number of streams when it is 1 to 4 (the loops over streams unroll to what is needed),
+// 0 for any number up to SN_MAX_STREAMS.
+template <typename TD, typename TO, int S_>
 __global__ void __launch_bounds__(SN_THREADS)
 stream_norm_kernel(float* h, int n_streams, const TD* __restrict__ delta, const float* __restrict__ mix,
                    const float* __restrict__ out_coef, const float* __restrict__ in_coef,
@@ -27,44 +29,55 @@ stream_norm_kernel(float* h, int n_streams, const TD* __restrict__ delta, const 
   extern __shared__ float u_s[];
   __shared__ float scratch[32];
   __shared__ float mix_s[SN_MAX_STREAMS * SN_MAX_STREAMS], oc_s[SN_MAX_STREAMS], ic_s[SN_MAX_STREAMS];
-  const int S = n_streams;
+  constexpr int SM = S_ > 0 ? S_ : SN_MAX_STREAMS;  // bound of the unrolled loops
+  const int S = S_ > 0 ? S_ : n_streams;
   if (threadIdx.x < S * S) mix_s[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S == threadIdx.x % S) ? 1.f : 0.f);
   if (threadIdx.x < S) {
     oc_s[threadIdx.x] = out_coef ? out_coef[threadIdx.x] : 1.f;
     ic_s[threadIdx.x] = in_coef ? in_coef[threadIdx.x] : 1.f;
   }
   __syncthreads();
+  // the coefficients in registers: the loops below are unrolled
+  float mx[SM][SM], oc[SM], ic[SM];
+#pragma unroll
+  for (int a = 0; a < SM; ++a) {
+    oc[a] = a < S ? oc_s[a] : 0.f;
+    ic[a] = a < S ? ic_s[a] : 0.f;
+#pragma unroll
+    for (int c = 0; c < SM; ++c) mx[a][c] = (a < S && c < S) ? mix_s[a * S + c] : 0.f;
+  }
   const size_t row = rows ? rows[blockIdx.x] : blockIdx.x;
   float* x = h + row * (size_t)S * dim;
   const bool store = delta != nullptr && rows == nullptr;
+  const bool has_mix = mix != nullptr, has_in = in_coef != nullptr;
   float sum = 0.f;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-    float xs[SN_MAX_STREAMS];
+    float xs[SM];
 #pragma unroll
-    for (int s = 0; s < SN_MAX_STREAMS; ++s) xs[s] = s < S ? x[(size_t)s * dim + d] : 0.f;
+    for (int s = 0; s < SM; ++s) xs[s] = s < S ? x[(size_t)s * dim + d] : 0.f;
     float u = 0.f;
     if (delta != nullptr) {
       const float y = to_f32<TD>(delta[row * dim + d]);
 #pragma unroll
-      for (int t = 0; t < SN_MAX_STREAMS; ++t) {
+      for (int t = 0; t < SM; ++t) {
         if (t < S) {
           float v = 0.f;
-          if (mix == nullptr) {
+          if (!has_mix) {
             v = xs[t];
           } else {
 #pragma unroll
-            for (int s = 0; s < SN_MAX_STREAMS; ++s)
-              if (s < S) v = fmaf(mix_s[s * S + t], xs[s], v);
+            for (int s = 0; s < SM; ++s)
+              if (s < S) v = fmaf(mx[s][t], xs[s], v);
           }
-          v = fmaf(oc_s[t], y, v);
+          v = fmaf(oc[t], y, v);
           if (store) x[(size_t)t * dim + d] = v;
-          u = in_coef ? fmaf(ic_s[t], v, u) : u + v;
+          u = has_in ? fmaf(ic[t], v, u) : u + v;
         }
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < SN_MAX_STREAMS; ++t)
-        if (t < S) u = in_coef ? fmaf(ic_s[t], xs[t], u) : u + xs[t];
+      for (int t = 0; t < SM; ++t)
+        if (t < S) u = has_in ? fmaf(ic[t], xs[t], u) : u + xs[t];
     }
     u_s[d] = u;
     sum += kind == 0 ? u : u * u;
@@ -103,12 +116,20 @@ extern "C" int fg_stream_norm(float* h, int n_streams, const void* delta, int de
   FG_CHECK_ARG(out == nullptr || w != nullptr, "fg_stream_norm: a norm needs its weight");
   const size_t smem = sizeof(float) * (size_t)dim;
   FG_CHECK_ARG(smem <= 200 * 1024, "fg_stream_norm: a row of %d does not fit shared memory", dim);
-#define LAUNCH(TD, TO)                                                                                       \
+#define LAUNCH_S(TD, TO, S)                                                                                  \
   do {                                                                                                       \
-    if (smem > 48 * 1024)                                                                                    \
-      cudaFuncSetAttribute(stream_norm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    stream_norm_kernel<TD, TO><<<n_rows, SN_THREADS, smem, stream>>>(                                        \
-        h, n_streams, (const TD*)delta, mix, out_coef, in_coef, w, b, (TO*)out, rows, dim, eps, kind);       \
+    auto kern = stream_norm_kernel<TD, TO, S>;                                                               \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    kern<<<n_rows, SN_THREADS, smem, stream>>>(h, n_streams, (const TD*)delta, mix, out_coef, in_coef, w, b, \
+                                               (TO*)out, rows, dim, eps, kind);                              \
+  } while (0)
+#define LAUNCH(TD, TO)                          \
+  do {                                          \
+    if (n_streams == 1) LAUNCH_S(TD, TO, 1);    \
+    else if (n_streams == 2) LAUNCH_S(TD, TO, 2); \
+    else if (n_streams == 3) LAUNCH_S(TD, TO, 3); \
+    else if (n_streams == 4) LAUNCH_S(TD, TO, 4); \
+    else LAUNCH_S(TD, TO, 0);                   \
   } while (0)
   const bool df = delta == nullptr || delta_dtype == FG_F32;
   if (df && out_dtype == FG_F32) LAUNCH(float, float);
@@ -116,6 +137,7 @@ extern "C" int fg_stream_norm(float* h, int n_streams, const void* delta, int de
   else if (!df && out_dtype == FG_F32) LAUNCH(__nv_bfloat16, float);
   else LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
+#undef LAUNCH_S
   FG_CHECK_LAUNCH("fg_stream_norm");
   return 0;
 }

@@ -339,6 +339,54 @@ def _mixer_times(cfg, device, timer: Timer, layer: int) -> Dict[str, float]:
     return out
 
 
+def _latent_attention_times(cfg, device, timer: Timer, layer: int) -> Dict[str, float]:
+    """The attention launches of a latent-attention layer alone (folded queries in, summed latents
+    out): a 2,048-token prompt, and 8 single tokens at position 2,048."""
+    from ..engine import StepEntry
+
+    engine = _engine(cfg, device, DECODE_BATCH, DECODE_CONTEXT)
+    _fill(engine)
+    mixer = engine.model.blocks[layer].mixer
+    memory = engine.memories[layer]
+    p = mixer.params
+    H, R, r, d = p.n_heads, p.kv_rank, p.rot_dim, p.head_dim
+    gen = torch.Generator().manual_seed(SEED)
+    out = {}
+
+    def context(entries):
+        reqs = engine._validate(entries)
+        for e, rq in zip(entries, reqs):
+            engine.cache.reserve(rq, rq.length + len(e.tokens))
+        engine.cache.flush_tables()
+        return engine.build_context(entries, reqs)
+
+    def run(t, ctx):
+        qa = torch.randn(H, t, R, generator=gen).to(device, torch.bfloat16)
+        q = torch.randn(t, H, d + r, generator=gen).to(device, torch.bfloat16)
+        gate = torch.randn(t, H, generator=gen).to(device, torch.bfloat16)
+        o = torch.empty_like(qa)
+        return timer.us(lambda: engine.ops.latent_attention(qa, q[:, :, d:], o, gate, memory, ctx, H, R, r, p.softmax_scale))
+
+    engine.admit("p")
+    us = run(PREFILL_TOKENS, context([StepEntry("p", [1] * PREFILL_TOKENS, [])]))
+    keys = PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2
+    out["prefill_us"] = round(us, 1)
+    out["prefill_tflops"] = round(2 * H * keys * (2 * R + r) / (us * 1e-6) / 1e12, 1)
+    engine.release("p")
+    ids = [f"d{i}" for i in range(DECODE_BATCH)]
+    for rid in ids:
+        rq = engine.admit(rid)
+        engine.cache.reserve(rq, DECODE_CONTEXT - 1)
+        engine.cache.advance(rq, DECODE_CONTEXT - 1)
+    us = run(DECODE_BATCH, context([StepEntry(rid, [1], []) for rid in ids]))
+    out["decode_us"] = round(us, 1)
+    out["decode_gbs"] = round(DECODE_BATCH * DECODE_CONTEXT * mixer.entry * 2 / (us * 1e-6) / 1e9, 1)
+    engine.ops.check_status()
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
 def zeladra_kernel_table(size, device, peaks) -> Dict[str, dict]:
     """The kernels of the Zeladra design alone at one size, each beside the like kernel of the
     Llama shape where there is one: microseconds and the fraction of the roofline."""
@@ -408,6 +456,8 @@ def zeladra_kernel_table(size, device, peaks) -> Dict[str, dict]:
     table[f"attention softmax (zeladra 'attention', window {window}, keeps 4)"] = _attention_times(z, device, timer, 2, window, *geometry)
     table[f"attention softmax (llama, window {window})"] = _attention_times(llama_config(*small, window=window), device, timer, 0,
                                                                           window, *geometry)
+    table["attention over the cached latent (zeladra 'latent_attention', causal)"] = _latent_attention_times(z, device, timer, 0)
+    table["attention softmax (llama, causal)"] = _attention_times(llama_config(*small), device, timer, 0, None, *geometry)
     for name, row in table.items():
         if "prefill_tflops" in row:
             row["prefill_tensor_frac"] = round(row["prefill_tflops"] * 1e12 / tensor, 3)
