@@ -213,8 +213,12 @@ def latent_mma_supported(rank: int, rot_dim: int) -> bool:
         and -(-(rank + rot_dim) // 16) * 16 <= 640
 
 
-def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> None:
-    """Compile every library (used by the build check and before shipping)."""
+def build_all(head_dims: Sequence[int] = (16, 32, 64, 128), latent_sizes: Sequence = ((512, 64), (256, 32))) -> None:
+    """Compile every library (used by the build check and before shipping); the latent-attention
+    library for the given (latent, rotated part) sizes."""
     _compile("fg_core", CORE_SOURCES)
+    for rank, rot in latent_sizes:
+        _compile(f"fg_latent_r{rank}_t{rot}", ["latent_mma.cu", "errors.cu"],
+                 [f"FG_LATENT_RANK={rank}", f"FG_LATENT_ROT={rot}"])
     for hd in head_dims:
         _compile(f"fg_attn_hd{hd}", ["attention.cu", "errors.cu"], [f"FG_HEAD_DIM={hd}"])

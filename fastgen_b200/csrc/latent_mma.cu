@@ -10,7 +10,7 @@
 // A block takes 64 (token, head) rows of one attention tile and, when the launch is split,
 // one stretch of its keys.  Four row warps own 16 rows each; with latents above 256 numbers a
 // second set of four warps owns the other half of the output columns (both sets compute the
-// scores).  Keys come in tiles of 64 (32 for entries above 256 numbers) through a two-stage
+// scores).  Keys come in tiles of 64 (32 for entries above 400 numbers) through a two-stage
 // cp.async ring.  Softmax statistics and the output accumulators are float32; the
 // probabilities are rounded to bfloat16 for the second product.
 //
@@ -37,7 +37,7 @@ constexpr int WN = R16 <= 256 ? 1 : 2;   // sets of warps over the output column
 constexpr int RW = R16 / WN;             // output columns a warp owns
 constexpr int LD = D16 + 8;
 constexpr int ROWS = 64;
-constexpr int KEYS = D16 <= 256 ? 64 : 32;
+constexpr int KEYS = D16 <= 400 ? 64 : 32;
 constexpr int NT = KEYS / 8;
 constexpr int NTHREADS = 128 * WN;
 constexpr int PART = R16 + 2;            // floats of a partial: the output, then maximum and sum

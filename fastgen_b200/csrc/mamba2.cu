@@ -9,7 +9,8 @@
 //   S <- a * S + dt * B x^T      (S is N x P, P the head's value size)
 //   y = S^T C + D[h] * x
 //
-// A request's state lives in one float32 row per slot: [heads, N, P] for S, then
+// A request's state lives in one float32 row per slot: [heads, P, N] for S (a column's rows side
+// by side, as the recurrence's threads hold them), then
 // [taps-1, channels] for the convolution's last inputs (oldest first).  It is zero at
 // admission, which is also "zeros before the start" for the convolution.  A step may bring a
 // sequence any number of tokens; sequences are consecutive runs of tokens with one slot, and
@@ -23,12 +24,14 @@
 // out[t, c] = silu(bias[c] + sum_k w[c, k] * in[t - (taps-1-k), c]); inputs before the step's
 // first token of the sequence come from the state.
 constexpr int CONV_THREADS = 128;
-constexpr int CONV_TOKENS = 32;
 constexpr int CONV_MAX_TAPS = 8;
 
-// A thread walks one channel over the block's tokens and keeps the last taps-1 inputs in
-// registers; they are fetched anew (from the step's tokens or from the state) only where a
-// sequence's part of the step begins or the block's stretch of tokens does.
+// A thread computes one channel of four consecutive tokens.  Nothing here waits for anything
+// else: the slots of the tokens around them are read first, then all the taps' inputs (from the
+// step's tokens, or from the state where a sequence's part of the step began less than taps-1
+// tokens ago), and neighbouring threads' re-reads hit the cache.
+constexpr int CONV_TOKENS = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(CONV_THREADS)
 conv_silu_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ out, long out_stride,
@@ -37,52 +40,46 @@ conv_silu_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ o
                  int taps) {
   const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
   if (c >= channels) return;
+  const int t0 = blockIdx.x * CONV_TOKENS;
+  constexpr int BACK = CONV_MAX_TAPS - 1;
+  int rq[CONV_TOKENS + BACK];  // rq[j]: the slot of token t0 - BACK + j
+#pragma unroll
+  for (int j = 0; j < CONV_TOKENS + BACK; ++j) {
+    const int t = t0 - BACK + j;
+    rq[j] = (t >= 0 && t < n_tokens) ? req[t] : -1;
+  }
   float wk[CONV_MAX_TAPS];
 #pragma unroll
   for (int k = 0; k < CONV_MAX_TAPS; ++k) wk[k] = k < taps ? w[(size_t)c * taps + k] : 0.f;
   const float bc = bias ? bias[c] : 0.f;
-  const int t0 = blockIdx.x * CONV_TOKENS;
-  float hist[CONV_MAX_TAPS];  // hist[j]: the input j + 1 tokens ago
+  float v[CONV_TOKENS][CONV_MAX_TAPS];
 #pragma unroll
-  for (int j = 0; j < CONV_MAX_TAPS; ++j) hist[j] = 0.f;
-  int prev_slot = -1;
-  for (int t = t0; t < min(t0 + CONV_TOKENS, n_tokens); ++t) {
-    const int slot = req[t];
-    if (slot < 0) {
-      prev_slot = -1;
-      continue;
-    }
-    if (slot != prev_slot) {
-      // how many of the taps-1 tokens before t the step itself brings
-      int have = 0;
-      while (have < taps - 1 && t - have - 1 >= 0 && req[t - have - 1] == slot) ++have;
-      const float* st = state + (size_t)slot * state_stride + conv_offset;
+  for (int u = 0; u < CONV_TOKENS; ++u) {
+    const int t = t0 + u, slot = rq[u + BACK];
+    // how many of the taps-1 tokens before t the step itself brings
+    int have = 0;
 #pragma unroll
-      for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
-        const int back = j + 1;
-        if (back < taps)
-          hist[j] = back <= have ? to_f32<T>(in[(size_t)(t - back) * in_stride + c])
-                                 : st[(size_t)(taps - 1 + have - back) * channels + c];
-      }
-      prev_slot = slot;
-    }
-    const float cur = to_f32<T>(in[(size_t)t * in_stride + c]);
-    float acc = bc;
+    for (int b = 1; b <= BACK; ++b)
+      if (have == b - 1 && b <= taps - 1 && rq[u + BACK - b] == slot) have = b;
 #pragma unroll
     for (int k = 0; k < CONV_MAX_TAPS; ++k) {
-      if (k < taps) {
+      v[u][k] = 0.f;
+      if (slot >= 0 && k < taps) {
         const int back = taps - 1 - k;  // this tap meets the input `back` tokens ago
-        float v = cur;
-#pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
-          if (back == j + 1) v = hist[j];
-        acc = fmaf(wk[k], v, acc);
+        v[u][k] = back <= have ? to_f32<T>(in[(size_t)(t - back) * in_stride + c])
+                               : state[(size_t)slot * state_stride + conv_offset +
+                                       (size_t)(taps - 1 + have - back) * channels + c];
       }
     }
-    out[(size_t)t * out_stride + c] = acc / (1.f + expf(-acc));
+  }
 #pragma unroll
-    for (int j = CONV_MAX_TAPS - 1; j > 0; --j) hist[j] = hist[j - 1];
-    hist[0] = cur;
+  for (int u = 0; u < CONV_TOKENS; ++u) {
+    if (rq[u + BACK] < 0) continue;
+    float acc = bc;
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; ++k)
+      if (k < taps) acc = fmaf(wk[k], v[u][k], acc);
+    out[(size_t)(t0 + u) * out_stride + c] = acc / (1.f + expf(-acc));
   }
 }
 
@@ -106,27 +103,29 @@ conv_state_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ 
 }
 
 // ---- the recurrence ---------------------------------------------------------------------------
-// A block works on (sequence, head, 16 columns of P); a thread on one column p and every
-// eighth row n of the state, which it keeps in registers.  Tokens are staged through shared
+// A block works on (sequence, head, 16 columns of P); LANES threads share a column p, each with
+// every LANES-th row n of the state in registers (8 threads a column for small states, a warp a
+// column from 64 rows on: the recurrence has heads * P * N independent chains and nothing else
+// to fill the GPU with).  Tokens are staged through shared
 // memory sixteen at a time in two buffers: while a stage is computed, the next one's B, C and x
 // arrive by asynchronous copies and its raw step sizes wait in a register.
 constexpr int SCAN_PB = 16;      // columns of P a block
-constexpr int SCAN_LANES = 8;    // threads a column
-constexpr int SCAN_THREADS = SCAN_PB * SCAN_LANES;
 constexpr int SCAN_TOKENS = 16;  // tokens a stage
+constexpr int SCAN_GROUP = 8;    // tokens whose sums are reduced together
 
 __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
                : "memory");
 }
 
-template <typename T, int NPT>
-__global__ void __launch_bounds__(SCAN_THREADS)
+template <typename T, int NPT, int SCAN_LANES>
+__global__ void __launch_bounds__(SCAN_PB * SCAN_LANES)
 ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restrict__ dt_raw, long dt_stride,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ y, long y_stride, float* __restrict__ state, long state_stride,
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int heads, int groups,
                 int N, int P) {
+  constexpr int SCAN_THREADS = SCAN_PB * SCAN_LANES;
   extern __shared__ float smem[];
   const int stage_floats = 2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS;
   auto Bs = [&](int buf) { return smem + buf * stage_floats; };               // [SCAN_TOKENS][N]
@@ -155,7 +154,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = lane + SCAN_LANES * i;
-    s[i] = (p_ok && n < N) ? S[(size_t)n * P + p] : 0.f;
+    s[i] = (p_ok && n < N) ? S[(size_t)p * N + n] : 0.f;
   }
 
   const int n_stages = (n_tok + SCAN_TOKENS - 1) / SCAN_TOKENS;
@@ -199,29 +198,46 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
     }
     __syncthreads();
     const float *bs = Bs(buf), *cs = Cs(buf), *xx = xs(buf), *dd = dts(buf), *de = decs(buf);
-    for (int tt = 0; tt < nt; ++tt) {
-      const float dt = dd[tt], dec = de[tt];
-      const float xv = xx[tt * SCAN_PB + pl];
-      const float dx = dt * xv;
-      float acc = 0.f;
+    // eight tokens at a time: their sums over the state's rows are reduced across the column's
+    // threads together, and thread j of the column stores token j's output
+    for (int tt0 = 0; tt0 < nt; tt0 += SCAN_GROUP) {
+      float acc[SCAN_GROUP];
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        const int n = lane + SCAN_LANES * i;
-        if (n < N) {
-          s[i] = fmaf(dec, s[i], bs[tt * N + n] * dx);
-          acc = fmaf(s[i], cs[tt * N + n], acc);
+      for (int u = 0; u < SCAN_GROUP; ++u) {
+        const int tt = tt0 + u;
+        float a0 = 0.f, a1 = 0.f;
+        if (tt < nt) {
+          const float dec = de[tt];
+          const float dx = dd[tt] * xx[tt * SCAN_PB + pl];
+#pragma unroll
+          for (int i = 0; i < NPT; ++i) {
+            const int n = lane + SCAN_LANES * i;
+            if (n < N) {
+              s[i] = fmaf(dec, s[i], bs[tt * N + n] * dx);
+              if (i & 1) a1 = fmaf(s[i], cs[tt * N + n], a1);
+              else a0 = fmaf(s[i], cs[tt * N + n], a0);
+            }
+          }
         }
+        acc[u] = a0 + a1;
       }
 #pragma unroll
-      for (int o = SCAN_LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane == 0 && p_ok) y[(size_t)(start + t0 + tt) * y_stride + h * P + p] = fmaf(dsk, xv, acc);
+      for (int o = SCAN_LANES / 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < SCAN_GROUP; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+      float mine = 0.f;
+#pragma unroll
+      for (int u = 0; u < SCAN_GROUP; ++u)
+        if (lane == u) mine = acc[u];
+      const int tt = tt0 + lane;
+      if (lane < SCAN_GROUP && tt < nt && p_ok) y[(size_t)(start + t0 + tt) * y_stride + h * P + p] = fmaf(dsk, xx[tt * SCAN_PB + pl], mine);
     }
     __syncthreads();  // the stage is read to its end before the copies after next overwrite it
   }
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = lane + SCAN_LANES * i;
-    if (p_ok && n < N) S[(size_t)n * P + p] = s[i];
+    if (p_ok && n < N) S[(size_t)p * N + n] = s[i];
   }
 }
 
@@ -251,6 +267,44 @@ gated_part_norm_kernel(const float* __restrict__ y, long y_stride, const T* __re
     const float zv = to_f32<T>(zr[d]);
     const float v = yr[d] * (zv / (1.f + expf(-zv)));
     out[(size_t)t * out_stride + c0 + d] = from_f32<T>(v * rstd * w[c0 + d]);
+  }
+}
+
+// Parts of up to 1,024 columns: a warp a (token, part), the part's values in registers between the
+// sum of squares and the scaling, so y and z are read once.
+constexpr int GW_WARPS = 8;
+constexpr int GW_ITEMS = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(GW_WARPS * 32)
+gated_part_norm_warp_kernel(const float* __restrict__ y, long y_stride, const T* __restrict__ z, long z_stride,
+                            const float* __restrict__ w, T* __restrict__ out, long out_stride,
+                            const int* __restrict__ req, int n_tokens, int parts, int part, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * GW_WARPS + (threadIdx.x >> 5);
+  if (item >= (long)n_tokens * parts) return;
+  const int t = item / parts, c0 = (item - (long)t * parts) * part;
+  if (req[t] < 0) return;
+  const float* yr = y + (size_t)t * y_stride + c0;
+  const T* zr = z + (size_t)t * z_stride + c0;
+  float v[GW_ITEMS];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < GW_ITEMS; ++i) {
+    const int d = lane + 32 * i;
+    v[i] = 0.f;
+    if (d < part) {
+      const float zv = to_f32<T>(zr[d]);
+      v[i] = yr[d] * (zv / (1.f + expf(-zv)));
+    }
+    ss += v[i] * v[i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = 1.f / sqrtf(ss / (float)part + eps);
+#pragma unroll
+  for (int i = 0; i < GW_ITEMS; ++i) {
+    const int d = lane + 32 * i;
+    if (d < part) out[(size_t)t * out_stride + c0 + d] = from_f32<T>(v[i] * rstd * w[c0 + d]);
   }
 }
 
@@ -296,25 +350,25 @@ static int launch_scan(const float* xbc, long xbc_stride, const T* dt_raw, long 
                        cudaStream_t stream) {
   const dim3 grid(n_seqs, heads, (P + SCAN_PB - 1) / SCAN_PB);
   const size_t smem = 2 * sizeof(float) * (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS);
-  const int npt = (N + SCAN_LANES - 1) / SCAN_LANES;
-#define SCAN(NPT)                                                                                               \
+  const int lanes = N >= 64 ? 32 : 8;
+  const int npt = (N + lanes - 1) / lanes;
+#define SCAN(NPT, LANES)                                                                                        \
   do {                                                                                                          \
-    if (smem > 48 * 1024)                                                                                       \
-      cudaFuncSetAttribute(ssm_scan_kernel<T, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    ssm_scan_kernel<T, NPT><<<grid, SCAN_THREADS, smem, stream>>>(xbc, xbc_stride, dt_raw, dt_stride, dt_bias,  \
-                                                                  a_log, d_skip, y, y_stride, state,            \
-                                                                  state_stride, seq_slot, seq_start, heads,     \
-                                                                  groups, N, P);                                \
+    auto kern = ssm_scan_kernel<T, NPT, LANES>;                                                                 \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    kern<<<grid, SCAN_PB * LANES, smem, stream>>>(xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, d_skip, y, \
+                                                  y_stride, state, state_stride, seq_slot, seq_start, heads,    \
+                                                  groups, N, P);                                                \
   } while (0)
-  if (npt <= 1) SCAN(1);
-  else if (npt <= 2) SCAN(2);
-  else if (npt <= 4) SCAN(4);
-  else if (npt <= 8) SCAN(8);
-  else if (npt <= 16) SCAN(16);
-  else if (npt <= 32) SCAN(32);
-  else {
-    fg_set_error("fg_mamba2_scan: a state of %d rows is more than the kernel takes (256)", N);
-    return -1;
+  if (lanes == 32) {
+    if (npt <= 2) SCAN(2, 32);
+    else if (npt <= 4) SCAN(4, 32);
+    else SCAN(8, 32);
+  } else {
+    if (npt <= 1) SCAN(1, 8);
+    else if (npt <= 2) SCAN(2, 8);
+    else if (npt <= 4) SCAN(4, 8);
+    else SCAN(8, 8);
   }
 #undef SCAN
   return 0;
@@ -350,6 +404,22 @@ extern "C" int fg_gated_part_norm(const float* y, long y_stride, const void* z, 
   if (n_tokens == 0) return 0;
   FG_CHECK_ARG(parts > 0 && width % parts == 0, "fg_gated_part_norm: %d columns in %d parts", width, parts);
   const dim3 grid(n_tokens, parts);
+  const int part = width / parts;
+  if (part <= 32 * GW_ITEMS) {
+    const long items = (long)n_tokens * parts;
+    const int blocks = (int)((items + GW_WARPS - 1) / GW_WARPS);
+    if (dtype == FG_F32)
+      gated_part_norm_warp_kernel<float><<<blocks, GW_WARPS * 32, 0, stream>>>(
+          y, y_stride, (const float*)z, z_stride, w, (float*)out, out_stride, req, n_tokens, parts, part, eps);
+    else if (dtype == FG_BF16)
+      gated_part_norm_warp_kernel<__nv_bfloat16><<<blocks, GW_WARPS * 32, 0, stream>>>(
+          y, y_stride, (const __nv_bfloat16*)z, z_stride, w, (__nv_bfloat16*)out, out_stride, req, n_tokens, parts,
+          part, eps);
+    else
+      FG_CHECK_ARG(false, "fg_gated_part_norm: bad dtype %d", dtype);
+    FG_CHECK_LAUNCH("fg_gated_part_norm");
+    return 0;
+  }
   if (dtype == FG_F32)
     gated_part_norm_kernel<float><<<grid, GN_THREADS, 0, stream>>>(y, y_stride, (const float*)z, z_stride,
                                                                     w, (float*)out, out_stride, req,

@@ -22,31 +22,37 @@ constexpr int SN_THREADS = 256;
 // 0 for any number up to SN_MAX_STREAMS.
 template <typename TD, typename TO, int S_>
 __global__ void __launch_bounds__(SN_THREADS)
-stream_norm_kernel(float* h, int n_streams, const TD* __restrict__ delta, const float* __restrict__ mix,
+stream_norm_kernel(float* h, int n_streams, const TD* delta, const float* __restrict__ mix,
                    const float* __restrict__ out_coef, const float* __restrict__ in_coef,
                    const float* __restrict__ w, const float* __restrict__ b, TO* __restrict__ out,
-                   const int* __restrict__ rows, int dim, float eps, int kind) {
+                   const int* rows, int dim, float eps, int kind) {
   extern __shared__ float u_s[];
   __shared__ float scratch[32];
-  __shared__ float mix_s[SN_MAX_STREAMS * SN_MAX_STREAMS], oc_s[SN_MAX_STREAMS], ic_s[SN_MAX_STREAMS];
   constexpr int SM = S_ > 0 ? S_ : SN_MAX_STREAMS;  // bound of the unrolled loops
   const int S = S_ > 0 ? S_ : n_streams;
-  if (threadIdx.x < S * S) mix_s[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S == threadIdx.x % S) ? 1.f : 0.f);
-  if (threadIdx.x < S) {
-    oc_s[threadIdx.x] = out_coef ? out_coef[threadIdx.x] : 1.f;
-    ic_s[threadIdx.x] = in_coef ? in_coef[threadIdx.x] : 1.f;
-  }
-  __syncthreads();
-  // the coefficients in registers: the loops below are unrolled
+  pdl_trigger();
+  // the coefficients are the model's: read (into registers, the loops below are unrolled) while
+  // the kernel before this one finishes; the streams and the summand are touched after the wait
   float mx[SM][SM], oc[SM], ic[SM];
 #pragma unroll
   for (int a = 0; a < SM; ++a) {
-    oc[a] = a < S ? oc_s[a] : 0.f;
-    ic[a] = a < S ? ic_s[a] : 0.f;
+    oc[a] = (a < S && out_coef) ? out_coef[a] : (a < S ? 1.f : 0.f);
+    ic[a] = (a < S && in_coef) ? in_coef[a] : (a < S ? 1.f : 0.f);
 #pragma unroll
-    for (int c = 0; c < SM; ++c) mx[a][c] = (a < S && c < S) ? mix_s[a * S + c] : 0.f;
+    for (int c = 0; c < SM; ++c) mx[a][c] = (a < S && c < S) ? (mix ? mix[a * S + c] : (a == c ? 1.f : 0.f)) : 0.f;
   }
-  const size_t row = rows ? rows[blockIdx.x] : blockIdx.x;
+  // a row of up to 8 x 256 columns: its weights wait in registers too
+  const bool small = dim <= 8 * SN_THREADS;
+  float w_r[8], b_r[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = threadIdx.x + i * SN_THREADS;
+    w_r[i] = (small && out != nullptr && d < dim) ? w[d] : 0.f;
+    b_r[i] = (small && out != nullptr && b != nullptr && d < dim) ? b[d] : 0.f;
+  }
+  const int* rows_v = rows;
+  pdl_wait();
+  const size_t row = rows_v ? ld_global_4(rows_v + blockIdx.x) : blockIdx.x;
   float* x = h + row * (size_t)S * dim;
   const bool store = delta != nullptr && rows == nullptr;
   const bool has_mix = mix != nullptr, has_in = in_coef != nullptr;
@@ -98,6 +104,14 @@ stream_norm_kernel(float* h, int n_streams, const TD* __restrict__ delta, const 
     rstd = 1.f / sqrtf(sum / (float)dim + eps);
   }
   TO* o = out + (size_t)blockIdx.x * dim;
+  if (small) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = threadIdx.x + i * SN_THREADS;
+      if (d < dim) o[d] = from_f32<TO>((u_s[d] - mean) * rstd * w_r[i] + b_r[i]);
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float v = (u_s[d] - mean) * rstd * w[d];
     if (b != nullptr) v += b[d];
@@ -120,8 +134,8 @@ extern "C" int fg_stream_norm(float* h, int n_streams, const void* delta, int de
   do {                                                                                                       \
     auto kern = stream_norm_kernel<TD, TO, S>;                                                               \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    kern<<<n_rows, SN_THREADS, smem, stream>>>(h, n_streams, (const TD*)delta, mix, out_coef, in_coef, w, b, \
-                                               (TO*)out, rows, dim, eps, kind);                              \
+    fg_launch_pdl(kern, dim3(n_rows), dim3(SN_THREADS), smem, stream, h, n_streams, (const TD*)delta, mix,   \
+                  out_coef, in_coef, w, b, (TO*)out, rows, dim, eps, kind);                                  \
   } while (0)
 #define LAUNCH(TD, TO)                          \
   do {                                          \
