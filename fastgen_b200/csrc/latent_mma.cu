@@ -41,6 +41,7 @@ constexpr int KEYS = D16 <= 400 ? 64 : 32;
 constexpr int NT = KEYS / 8;
 constexpr int NTHREADS = 128 * WN;
 constexpr int PART = R16 + 2;            // floats of a partial: the output, then maximum and sum
+constexpr int MERGE_SPLITS = 256;        // most stretches a launch may be cut into
 static_assert(R % 8 == 0 && ROT % 2 == 0, "latents are multiples of 8, rotated parts of 2");
 static_assert(RW % 16 == 0, "a warp's output columns come in sixteens");
 
@@ -84,17 +85,22 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, long qa_ts, lo
     return;
   }
   if (tid < ROWS) row_pos[tid] = row_valid(tid) ? pos[tok0 + row_token(tid)] : -1;
-  // queries -> shared memory: [qa | qt | zeros], zero rows where the tile is not full
+  // queries -> shared memory: [qa | qt | zeros], zero rows where the tile is not full; asynchronous
+  // 4-byte copies, all in flight at once (a tile of single tokens is mostly this load)
   for (int i = tid; i < ROWS * (D16 / 2); i += NTHREADS) {
     const int r = i / (D16 / 2), col = 2 * (i - r * (D16 / 2));
-    __nv_bfloat162 v = __floats2bfloat162_rn(0.f, 0.f);
-    if (row_valid(r) && col < D) {
+    const bool ok = row_valid(r) && col < D;
+    const __nv_bfloat16* src = qa;
+    if (ok) {
       const size_t tk = tok0 + row_token(r), hh = row_head(r);
-      v = col < R ? *reinterpret_cast<const __nv_bfloat162*>(qa + tk * qa_ts + hh * qa_hs + col)
-                  : *reinterpret_cast<const __nv_bfloat162*>(qt + tk * qt_ts + hh * qt_hs + (col - R));
+      src = col < R ? qa + tk * qa_ts + hh * qa_hs + col : qt + tk * qt_ts + hh * qt_hs + (col - R);
     }
-    *reinterpret_cast<__nv_bfloat162*>(Qs + r * LD + col) = v;
+    const int bytes = ok ? 4 : 0;  // 0: zero-filled, nothing is read
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_u32(Qs + r * LD + col)), "l"(src), "r"(bytes)
+                 : "memory");
   }
+  cp_async_commit();
+  cp_async_wait<0>();
   __syncthreads();
   int max_pos = -1;
   for (int r = 0; r < ROWS; r += heads_per_block) max_pos = max(max_pos, row_pos[r]);  // rows are ordered by token
@@ -246,21 +252,32 @@ latent_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict
     return;
   }
   const float* base = scratch + ((size_t)ts * ROWS + r) * n_splits * PART;
-  float mm = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, base[(size_t)s * PART + R16]);
-  float ll = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = base[(size_t)s * PART + R16];
-    if (ms != -INFINITY) ll += exp2f(ms - mm) * base[(size_t)s * PART + R16 + 1];
+  // the stretches' weights once a block (the launcher allows up to MERGE_SPLITS of them)
+  __shared__ float wgt_s[MERGE_SPLITS];
+  __shared__ float f_s;
+  if (threadIdx.x < 32) {
+    float mm = -INFINITY;
+    for (int s = threadIdx.x; s < n_splits; s += 32) mm = fmaxf(mm, base[(size_t)s * PART + R16]);
+    mm = warp_max(mm);
+    float ll = 0.f;
+    for (int s = threadIdx.x; s < n_splits; s += 32) {
+      const float ms = base[(size_t)s * PART + R16];
+      const float wg = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+      wgt_s[s] = wg;
+      ll += wg * base[(size_t)s * PART + R16 + 1];
+    }
+    ll = warp_sum(ll);
+    if (threadIdx.x == 0) {
+      float f = ll > 0.f ? 1.f / ll : 0.f;
+      if (gate != nullptr) f *= 1.f / (1.f + __expf(-__bfloat162float(gate[tk * gate_ts + head])));
+      f_s = f;
+    }
   }
-  float f = ll > 0.f ? 1.f / ll : 0.f;
-  if (gate != nullptr) f *= 1.f / (1.f + __expf(-__bfloat162float(gate[tk * gate_ts + head])));
+  __syncthreads();
+  const float f = f_s;
   for (int d = threadIdx.x; d < R; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = base[(size_t)s * PART + R16];
-      if (ms != -INFINITY) acc += exp2f(ms - mm) * base[(size_t)s * PART + d];
-    }
+    for (int s = 0; s < n_splits; ++s) acc = fmaf(wgt_s[s], base[(size_t)s * PART + d], acc);
     dst[d] = __float2bfloat16_rn(acc * f);
   }
 }
@@ -292,7 +309,7 @@ extern "C" int fg_latent_attention_mma(const void* qa, long qa_ts, long qa_hs, c
   FG_CHECK_ARG(rank == R && rot_dim == ROT && entry == E,
                "fg_latent_attention_mma: library built for a latent of %d + %d (entries of %d), got %d + %d (%d)", R,
                ROT, E, rank, rot_dim, entry);
-  FG_CHECK_ARG(n_splits >= 1 && n_splits <= 65535 && keys_per_split > 0 && keys_per_split % KEYS == 0,
+  FG_CHECK_ARG(n_splits >= 1 && n_splits <= MERGE_SPLITS && keys_per_split > 0 && keys_per_split % KEYS == 0,
                "fg_latent_attention_mma: %d stretches of %d keys", n_splits, keys_per_split);
   FG_CHECK_ARG(scratch_floats >= fg_latent_mma_scratch_floats(n_tiles, n_heads, n_splits),
                "fg_latent_attention_mma: scratch of %lld floats is too small", scratch_floats);
