@@ -158,24 +158,18 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
   }
 
   const int n_stages = (n_tok + SCAN_TOKENS - 1) / SCAN_TOKENS;
-  // a stage is always whole: the places of tokens the sequence does not have hold zeros (and a
-  // decay of one), which leave the state as it is, so the loops below have no conditions
   auto issue = [&](int k) {
     const int buf = k & 1, t0 = k * SCAN_TOKENS, nt = min(SCAN_TOKENS, n_tok - t0);
     float *bs = Bs(buf), *cs = Cs(buf), *xx = xs(buf);
-    for (int i = tid; i < SCAN_TOKENS * N; i += SCAN_THREADS) {
+    for (int i = tid; i < nt * N; i += SCAN_THREADS) {
       const int tt = i / N, n = i - tt * N;
-      if (tt < nt) {
-        const float* row = xbc + (size_t)(start + t0 + tt) * xbc_stride + inner + g * N + n;
-        cp_async_4(bs + i, row);
-        cp_async_4(cs + i, row + groups * N);
-      } else {
-        bs[i] = cs[i] = 0.f;
-      }
+      const float* row = xbc + (size_t)(start + t0 + tt) * xbc_stride + inner + g * N + n;
+      cp_async_4(bs + i, row);
+      cp_async_4(cs + i, row + groups * N);
     }
-    for (int i = tid; i < SCAN_TOKENS * SCAN_PB; i += SCAN_THREADS) {
+    for (int i = tid; i < nt * SCAN_PB; i += SCAN_THREADS) {
       const int tt = i / SCAN_PB, pp = i - tt * SCAN_PB;
-      if (tt < nt && p0 + pp < P) cp_async_4(xx + i, xbc + (size_t)(start + t0 + tt) * xbc_stride + h * P + p0 + pp);
+      if (p0 + pp < P) cp_async_4(xx + i, xbc + (size_t)(start + t0 + tt) * xbc_stride + h * P + p0 + pp);
       else xx[i] = 0.f;
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -189,11 +183,11 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
 
   for (int k = 0; k < n_stages; ++k) {
     const int buf = k & 1, t0 = k * SCAN_TOKENS, nt = min(SCAN_TOKENS, n_tok - t0);
-    if (tid < SCAN_TOKENS) {
+    if (tid < nt) {
       const float v = dtr + bias;
-      const float dt = tid < nt ? (v > 20.f ? v : log1pf(expf(v))) : 0.f;
+      const float dt = v > 20.f ? v : log1pf(expf(v));
       dts(buf)[tid] = dt;
-      decs(buf)[tid] = tid < nt ? expf(a * dt) : 1.f;
+      decs(buf)[tid] = expf(a * dt);
     }
     if (k + 1 < n_stages) {
       issue(k + 1);
@@ -212,15 +206,17 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
       for (int u = 0; u < SCAN_GROUP; ++u) {
         const int tt = tt0 + u;
         float a0 = 0.f, a1 = 0.f;
-        const float dec = de[tt];
-        const float dx = dd[tt] * xx[tt * SCAN_PB + pl];
+        if (tt < nt) {
+          const float dec = de[tt];
+          const float dx = dd[tt] * xx[tt * SCAN_PB + pl];
 #pragma unroll
-        for (int i = 0; i < NPT; ++i) {
-          const int n = lane + SCAN_LANES * i;
-          if (NPT * SCAN_LANES == N || n < N) {
-            s[i] = fmaf(dec, s[i], bs[tt * N + n] * dx);
-            if (i & 1) a1 = fmaf(s[i], cs[tt * N + n], a1);
-            else a0 = fmaf(s[i], cs[tt * N + n], a0);
+          for (int i = 0; i < NPT; ++i) {
+            const int n = lane + SCAN_LANES * i;
+            if (n < N) {
+              s[i] = fmaf(dec, s[i], bs[tt * N + n] * dx);
+              if (i & 1) a1 = fmaf(s[i], cs[tt * N + n], a1);
+              else a0 = fmaf(s[i], cs[tt * N + n], a0);
+            }
           }
         }
         acc[u] = a0 + a1;
