@@ -241,6 +241,143 @@ ssm_scan_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restr
   }
 }
 
+// ---- the recurrence, states of 64, 128 or 256 rows ------------------------------------------------
+// The same recurrence with fewer instructions a state element: N = 32 * NPT is a compile-time
+// number (no bounds to test, every address an immediate), B and C of a token sit side by side in
+// shared memory (one 8-byte load brings both), a warp owns two columns of P (a loaded pair serves
+// both), and the sums of 8 tokens x 2 columns over the state's rows are reduced by halving
+// exchanges (16 shuffles for the 16 sums) that leave sum k in lanes 2k and 2k + 1.
+constexpr int TS_COLS = 2;                       // columns of P a warp
+constexpr int TS_WARPS = SCAN_PB / TS_COLS;      // warps a block
+constexpr int TS_THREADS = 32 * TS_WARPS;
+
+template <typename T, int NPT>
+__global__ void __launch_bounds__(TS_THREADS)
+ssm_scan_tiled_kernel(const float* __restrict__ xbc, long xbc_stride, const T* __restrict__ dt_raw, long dt_stride,
+                      const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                      const float* __restrict__ d_skip, float* __restrict__ y, long y_stride,
+                      float* __restrict__ state, long state_stride, const int* __restrict__ seq_slot,
+                      const int* __restrict__ seq_start, int heads, int groups, int P) {
+  constexpr int N = 32 * NPT;
+  constexpr int STAGE = 2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS;  // floats
+  extern __shared__ __align__(16) float smem[];
+  auto BC = [&](int buf) { return reinterpret_cast<float2*>(smem + buf * STAGE); };      // [TOKENS][N] (B, C)
+  auto xs = [&](int buf) { return smem + buf * STAGE + 2 * SCAN_TOKENS * N; };           // [TOKENS][SCAN_PB]
+  auto dts = [&](int buf) { return xs(buf) + SCAN_TOKENS * SCAN_PB; };
+  auto decs = [&](int buf) { return dts(buf) + SCAN_TOKENS; };
+
+  const int slot = seq_slot[blockIdx.x];
+  if (slot < 0) return;
+  const int start = seq_start[blockIdx.x], n_tok = seq_start[blockIdx.x + 1] - start;
+  if (n_tok <= 0) return;
+  const int h = blockIdx.y, g = h / (heads / groups);
+  const int p0 = blockIdx.z * SCAN_PB;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int pc = p0 + TS_COLS * warp;  // this warp's first column
+  const int inner = heads * P;
+  const float bias = dt_bias[h];
+  const float a = -expf(a_log[h]);
+  const float dsk = d_skip[h];
+
+  float* S = state + (size_t)slot * state_stride + (size_t)h * N * P;
+  float s[TS_COLS][NPT];
+#pragma unroll
+  for (int c = 0; c < TS_COLS; ++c)
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) s[c][i] = pc + c < P ? S[(size_t)(pc + c) * N + lane + 32 * i] : 0.f;
+
+  const int n_stages = (n_tok + SCAN_TOKENS - 1) / SCAN_TOKENS;
+  auto issue = [&](int k) {
+    const int buf = k & 1, t0 = k * SCAN_TOKENS, nt = min(SCAN_TOKENS, n_tok - t0);
+    float* bc = smem + buf * STAGE;
+    float* xx = xs(buf);
+    for (int i = tid; i < nt * N; i += TS_THREADS) {
+      const int tt = i / N, n = i - tt * N;
+      const float* row = xbc + (size_t)(start + t0 + tt) * xbc_stride + inner + g * N + n;
+      cp_async_4(bc + 2 * i, row);
+      cp_async_4(bc + 2 * i + 1, row + groups * N);
+    }
+    for (int i = tid; i < nt * SCAN_PB; i += TS_THREADS) {
+      const int tt = i / SCAN_PB, pp = i - tt * SCAN_PB;
+      if (p0 + pp < P) cp_async_4(xx + i, xbc + (size_t)(start + t0 + tt) * xbc_stride + h * P + p0 + pp);
+      else xx[i] = 0.f;
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  auto raw_dt = [&](int k) {
+    const int t = k * SCAN_TOKENS + tid;
+    return (tid < SCAN_TOKENS && t < n_tok) ? to_f32<T>(dt_raw[(size_t)(start + t) * dt_stride + h]) : 0.f;
+  };
+  issue(0);
+  float dtr = raw_dt(0);
+
+  for (int k = 0; k < n_stages; ++k) {
+    const int buf = k & 1, t0 = k * SCAN_TOKENS, nt = min(SCAN_TOKENS, n_tok - t0);
+    if (tid < nt) {
+      const float v = dtr + bias;
+      const float dt = v > 20.f ? v : log1pf(expf(v));
+      dts(buf)[tid] = dt;
+      decs(buf)[tid] = expf(a * dt);
+    }
+    if (k + 1 < n_stages) {
+      issue(k + 1);
+      dtr = raw_dt(k + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();
+    const float2* bc = BC(buf);
+    const float *xx = xs(buf), *dd = dts(buf), *de = decs(buf);
+    for (int tt0 = 0; tt0 < nt; tt0 += SCAN_GROUP) {
+      float acc[TS_COLS * SCAN_GROUP];  // [column][token of the group]
+#pragma unroll
+      for (int u = 0; u < SCAN_GROUP; ++u) {
+        const int tt = tt0 + u;
+        float a0 = 0.f, a1 = 0.f;
+        if (tt < nt) {
+          const float dec = de[tt], dtv = dd[tt];
+          const float2 xv = *reinterpret_cast<const float2*>(xx + tt * SCAN_PB + TS_COLS * warp);
+          const float dx0 = dtv * xv.x, dx1 = dtv * xv.y;
+#pragma unroll
+          for (int i = 0; i < NPT; ++i) {
+            const float2 v = bc[tt * N + lane + 32 * i];
+            s[0][i] = fmaf(dec, s[0][i], v.x * dx0);
+            a0 = fmaf(s[0][i], v.y, a0);
+            s[1][i] = fmaf(dec, s[1][i], v.x * dx1);
+            a1 = fmaf(s[1][i], v.y, a1);
+          }
+        }
+        acc[u] = a0;
+        acc[SCAN_GROUP + u] = a1;
+      }
+      // halving exchanges: after the step with mask m a lane keeps the half of its sums that its
+      // bit m chooses, with the partner's share added
+#pragma unroll
+      for (int half = TS_COLS * SCAN_GROUP / 2, mask = 16; half >= 1; half >>= 1, mask >>= 1) {
+        const bool upper = (lane & mask) != 0;
+#pragma unroll
+        for (int j = 0; j < half; ++j) {
+          const float send = upper ? acc[j] : acc[j + half];
+          const float keep = upper ? acc[j + half] : acc[j];
+          acc[j] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+        }
+      }
+      acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);  // (16 sums use the masks 16, 8, 4, 2)
+      const int kidx = (lane >> 1) & 15, c = kidx >> 3, tt = tt0 + (kidx & 7);
+      if (!(lane & 1) && tt < nt && pc + c < P)
+        y[(size_t)(start + t0 + tt) * y_stride + h * P + pc + c] =
+            fmaf(dsk, xx[tt * SCAN_PB + TS_COLS * warp + c], acc[0]);
+    }
+    __syncthreads();  // the stage is read to its end before the copies after next overwrite it
+  }
+#pragma unroll
+  for (int c = 0; c < TS_COLS; ++c)
+#pragma unroll
+    for (int i = 0; i < NPT; ++i)
+      if (pc + c < P) S[(size_t)(pc + c) * N + lane + 32 * i] = s[c][i];
+}
+
 // ---- gate, then RMS norm in equal parts ---------------------------------------------------------
 // out[t, part] = v * rsqrt(mean(v^2) + eps) * w with v = y * silu(z) over the part's columns.
 constexpr int GN_THREADS = 256;
@@ -350,6 +487,22 @@ static int launch_scan(const float* xbc, long xbc_stride, const T* dt_raw, long 
                        cudaStream_t stream) {
   const dim3 grid(n_seqs, heads, (P + SCAN_PB - 1) / SCAN_PB);
   const size_t smem = 2 * sizeof(float) * (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS);
+  if (N == 64 || N == 128 || N == 256) {
+    const size_t tsmem = 2 * sizeof(float) * (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_PB + 2 * SCAN_TOKENS);
+#define TILED(NPT)                                                                                              \
+  do {                                                                                                          \
+    auto kern = ssm_scan_tiled_kernel<T, NPT>;                                                                  \
+    if (tsmem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem); \
+    kern<<<grid, TS_THREADS, tsmem, stream>>>(xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, d_skip, y,    \
+                                              y_stride, state, state_stride, seq_slot, seq_start, heads,        \
+                                              groups, P);                                                       \
+  } while (0)
+    if (N == 64) TILED(2);
+    else if (N == 128) TILED(4);
+    else TILED(8);
+#undef TILED
+    return 0;
+  }
   const int lanes = N >= 64 ? 32 : 8;
   const int npt = (N + lanes - 1) / lanes;
 #define SCAN(NPT, LANES)                                                                                        \

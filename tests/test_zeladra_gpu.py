@@ -365,7 +365,7 @@ def _tol(dtype):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(4, 24, 12, 2, 4, 2), (3, 16, 40, 3, 2, 1), (3, 40, 9, 1, 1, 3), (2, 64, 128, 1, 3, 2),
-                                   (1, 8, 1, 1, 8, 1)])
+                                   (1, 8, 1, 1, 8, 1), (2, 24, 64, 2, 2, 1), (1, 17, 256, 1, 2, 1), (2, 16, 200, 1, 2, 2)])
 def test_state_space_mixer_alone(dtype, sizes):
     """Convolution, recurrence, gate and norm in parts: a prompt portion, single tokens and short
     portions through the state of a slot; then the slot is used again and starts from zero."""
