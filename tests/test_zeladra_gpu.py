@@ -528,6 +528,61 @@ def test_replay(tmp_path, name, dtype, plan):
     assert engine.cache.n_live == 0 and all(f == g.pool.n_pages for f, g in zip(engine.cache.free_pages(), engine.cache.groups))
 
 
+def _random_config(seed):
+    """A configuration drawn at random: layer kinds in any order, sizes that pad and sizes that do not,
+    windows shorter and longer than the pages, kept positions beyond a window, latent layers that
+    read an earlier one's cache, one to four streams or the ordinary one."""
+    import random
+
+    rng = random.Random(seed)
+    layers, latents = [], []
+    for i in range(rng.randint(3, 7)):
+        kind = rng.choice(["latent_attention", "mamba2", "attention"])
+        if kind == "attention":
+            dim = rng.choice([16, 32, 48, 64])
+            kv = rng.choice([1, 2, 4])
+            mask = rng.choice([None, 1, 7, 40, 72, 130])
+            m = _attn(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([dim, 16, 32]), dim ** -0.5, dims=rng.choice([dim, dim // 2, 8]),
+                      base=rng.choice([1e4, 1e6]), mask=mask, keep=rng.choice([None, 0, 1, 4, 20, 70]) if mask else None)
+        elif kind == "mamba2":
+            heads = rng.choice([1, 2, 4, 6])
+            vdim = rng.choice([8, 16, 24, 48])
+            m = _ssm(heads, vdim, rng.choice([8, 16, 48, 64, 128]), rng.choice([g for g in (1, 2, 3) if heads % g == 0]),
+                     rng.choice([1, 2, 4, 5]), rng.choice([q for q in (1, 2, 3, 4) if (heads * vdim) % q == 0]))
+        else:
+            src = rng.choice(latents) if latents and rng.random() < 0.4 else None
+            heads, d, dv, qr = rng.choice([2, 4, 8]), rng.choice([16, 32]), rng.choice([16, 32, 64]), rng.choice([32, 64])
+            if src is not None:
+                b = layers[src]["mixer"]
+                sc = tuple(b["rot"]["scaling"].values()) if "scaling" in b["rot"] else None
+                m = _latent(heads, d, b["rot_dim"], dv, qr, b["kv_rank"], 0.12, b["rot"]["base"], sc, kv_from=src)
+            else:
+                sc = rng.choice([None, (2.0, 1024, 32.0, 1.0), (4.0, 64, 8.0, 1.0)])
+                m = _latent(heads, d, rng.choice([4, 8, 16, 32]), dv, qr, rng.choice([32, 64, 128, 256]), 0.12,
+                            rng.choice([1e4, 1e6]), sc)
+                latents.append(i)
+        layers.append(_layer(kind, m, rng.choice([None, 64, 136])))
+    cfg = dict(architecture="Zeladra", vocab=rng.choice([97, 211, 256]), width=rng.choice([64, 96, 200]),
+               norm=dict(eps=1e-5), embedding=dict(scale=rng.choice([0.5, 1.3])), layers=layers)
+    streams = rng.choice([None, 1, 2, 3, 4])
+    if streams is not None:
+        cfg["streams"] = streams
+    return cfg
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("seed", [11, 13, 25, 35, 37])
+def test_configurations_drawn_at_random(tmp_path, dtype, seed):
+    """Mixed batches of a model whose layers and sizes are drawn at random."""
+    cfg = _random_config(seed)
+    d = write_random_model(Path(tmp_path) / "m", cfg, seed, dtype=torch.bfloat16, norm_jitter=0.3, std=0.08)
+    requests = _requests(cfg["vocab"], [150, 33, 1, 90, 18, 2], 40 + seed)
+    steps = H.plan_mixed(requests, seed=seed)
+    outputs, engine = H.run_engine(d, dtype, steps, 64, H.max_live_tokens(steps, 64) + 64)
+    compare(d, requests, H.collect(steps, outputs), dtype)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("name", ["za", "zc"])
