@@ -453,8 +453,9 @@ class Ops:
             blocks = tiles.n * -(-n_heads // min(n_heads, rows))
             n_splits = 1
             if blocks < 96:
-                # few blocks: stretches of a key tile or two, until the launch fills the GPU twice over
-                n_splits = max(1, min(-(-max_keys // keys), -(-592 // blocks), 64))
+                # few blocks: stretches of key tiles, as many as give every SM one block (the large
+                # latents' blocks are alone on their SM, so more would be a second wave)
+                n_splits = max(1, min(-(-max_keys // keys), 148 // blocks, 64))
             per = -(-(-(-max_keys // n_splits)) // keys) * keys
             n_splits = -(-max_keys // per)
             floats = lib.fg_latent_mma_scratch_floats(tiles.n, n_heads, n_splits)
