@@ -412,7 +412,7 @@ extern "C" int fg_attention_prefill_tma_bf16(const void* q, int q_stride, void* 
                                              int n_pages, const int* pos, const int* tile_req,
                                              const int* tile_tok0, const int* tile_ntok, int n_tiles,
                                              int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                                             int* status, cudaStream_t stream) {
+                                             int keep_first, int* status, cudaStream_t stream) {
   using namespace fg_tma;
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_tma_bf16: library built for head size %d, got %d",
@@ -441,7 +441,7 @@ extern "C" int fg_attention_prefill_tma_bf16(const void* q, int q_stride, void* 
   kern<<<grid, PF_THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                            out_stride, block_table, table_width, page_size, n_pages, pos,
                                            tile_req, tile_tok0, tile_ntok, n_tiles, group, hpb, window,
-                                           scale * 1.4426950408889634f, status);
+                                           scale * 1.4426950408889634f, status, keep_first);
   FG_CHECK_LAUNCH("fg_attention_prefill_tma_bf16");
   return 0;
 }

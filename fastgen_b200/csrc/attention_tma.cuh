@@ -669,7 +669,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              int table_width, int page_size, int n_pages, const int* __restrict__ pos,
                              const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
                              const int* __restrict__ tile_ntok, int n_tiles_total, int group,
-                             int heads_per_block, int window, float scale_log2, int* status) {
+                             int heads_per_block, int window, float scale_log2, int* status, int keep_first) {
   static_assert(HD % 64 == 0, "tiled loads take 64-element halves");
   constexpr int LD = Tile<HD>::LD;
   constexpr int NT = PF_KEYS / 8;
@@ -723,7 +723,12 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int k_begin = window > 0 ? max(0, min_pos - window + 1) : 0;
   const int k_lo = k_begin / PF_KEYS * PF_KEYS;
   const int k_end = max_pos + 1;
-  const int n_tiles = (k_end - k_lo + PF_KEYS - 1) / PF_KEYS;
+  // with a window, the sequence's first keep_first positions stay visible: the key tiles that
+  // hold them and lie wholly before the window's first tile are walked first
+  if (window <= 0) keep_first = 0;
+  const int n_keep = keep_first > 0 ? min(k_lo, (keep_first + PF_KEYS - 1) / PF_KEYS * PF_KEYS) / PF_KEYS : 0;
+  const int n_tiles = n_keep + (k_end - k_lo + PF_KEYS - 1) / PF_KEYS;
+  auto tile_k0 = [&](int t) { return t < n_keep ? t * PF_KEYS : k_lo + (t - n_keep) * PF_KEYS; };
   const int* table_row = block_table + (size_t)b * table_width;
   const int box_rows = min(page_size, PF_KEYS);
   const int n_boxes = PF_KEYS / box_rows;
@@ -735,9 +740,9 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   auto fill_pages = [&](int t_first) {
     const int n = min(tiles_per_fill, n_tiles - t_first) * n_boxes;
     for (int x = tid; x < n; x += PF_THREADS) {
-      const int j0 = k_lo + t_first * PF_KEYS + x * box_rows;
+      const int j0 = tile_k0(t_first + x / n_boxes) + (x % n_boxes) * box_rows;
       int page = -1;
-      if (j0 < k_end && j0 + box_rows > k_begin) {
+      if (j0 < k_end && (j0 + box_rows > k_begin || j0 < keep_first)) {
         const int logical = j0 / page_size;
         page = logical < table_width ? table_row[logical] : -1;
         if (page < 0 || page >= n_pages) {
@@ -757,7 +762,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
     for (int i = 0; i < n_boxes; ++i) n_valid += box_page(t, i) >= 0;
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     mbar_arrive_expect(&full[stage], 2 * n_valid * box_rows * HD * 2);
-    const int slot0 = (k_lo + t * PF_KEYS) % page_size;
+    const int slot0 = tile_k0(t) % page_size;
     for (int i = 0; i < n_boxes; ++i) {
       const int page = box_page(t, i);
       if (page < 0) continue;
@@ -821,14 +826,14 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
     }
     if (t + 1 < n_tiles && tid == 0) issue(t + 1);  // its stage was released by the barrier below
     mbar_wait(&full[t & 1], (t >> 1) & 1, status, &gave_up);
-    const int k0 = k_lo + t * PF_KEYS;
+    const int k0 = tile_k0(t);
     if (k0 <= warp_max) {
       const unsigned char* ks = Ks + (t & 1) * STAGE_BYTES;
       const unsigned char* vs = Vs + (t & 1) * STAGE_BYTES;
       float s[NT][4];
       qk_product_swz<HD, NT, PF_HALF>(s, qf, ks, 0, lane);
       // only tiles that touch the diagonal, the window's edge or an unused row need the mask
-      const bool need_mask = !warp_full || k0 + PF_KEYS - 1 > warp_min ||
+      const bool need_mask = !warp_full || k0 + PF_KEYS - 1 > warp_min || t < n_keep ||
                              (window > 0 && k0 <= warp_max - window);
       if (need_mask) {
 #pragma unroll
@@ -837,7 +842,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
           for (int e = 0; e < 4; ++e) {
             const int j = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
             const int p = (e < 2) ? p0 : p1;
-            const bool vis = p >= 0 && j <= p && (window <= 0 || j > p - window);
+            const bool vis = p >= 0 && j <= p && (window <= 0 || j > p - window || j < keep_first);
             if (!vis) s[nt][e] = -INFINITY;
           }
       }

@@ -86,7 +86,7 @@ _ATTN_SIGNATURES = {
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
                                  ctypes.c_longlong, _I, _P, _P, _P],
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _P, _P],
+                                      _I, _F, _I, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P, _P, _I, _I, _P, _I, _P, _P],
     "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I, _I],
@@ -745,9 +745,10 @@ class Ops:
                 n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale),
                 _ptr(self.status), _stream()))
             return False
-        # windows that keep a sequence's first positions visible run on the mma.sync kernels, which
-        # walk the tiles of the kept positions before those of the window
-        use_tma = memory.tensor_maps is not None and not keep_first
+        # windows that keep a sequence's first positions visible run on the mma.sync kernels (on TMA
+        # tiles for prompts where the pools have tensor maps), which walk the tiles of the kept
+        # positions before those of the window
+        use_tma = memory.tensor_maps is not None
         rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
         tiling = attention_tiling(n_heads, n_kv_heads, rows)
         tiles = ctx.attention_tiles(tiling, 2)
@@ -758,7 +759,7 @@ class Ops:
                     memory.tensor_maps[3].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
                     page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
                     _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale))
-            if head_dim in (64, 128) and self.use_tcgen05:
+            if head_dim in (64, 128) and self.use_tcgen05 and not keep_first:
                 max_keys = -1 if tiles.max_keys is None else tiles.max_keys
                 # a captured list has padding: what a step of prompt tokens only would hold
                 nominal = 0 if tiles.count is None else max(1, -(-q.shape[0] // tiling))
@@ -768,7 +769,7 @@ class Ops:
                     *args, _ptr(self._work_counter), _ptr(scratch), _ptr(flags), room, max_keys,
                     _ptr(tiles.count), nominal, _ptr(self.status), _stream()))
             else:
-                _check(lib, lib.fg_attention_prefill_tma_bf16(*args, _ptr(self.status), _stream()))
+                _check(lib, lib.fg_attention_prefill_tma_bf16(*args, keep_first, _ptr(self.status), _stream()))
         elif tiles.n:
             _check(lib, lib.fg_attention_prefill_bf16(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
@@ -780,7 +781,7 @@ class Ops:
         turn = _ptr(out_freqs) if fused else None
         if singles.n:
             max_splits = max(1, -(-singles.max_len // DECODE_SPLIT))
-            tma = use_tma and n_heads // n_kv_heads <= 16
+            tma = use_tma and n_heads // n_kv_heads <= 16 and not keep_first
             # the persistent kernel numbers its partials by the (request, split) pairs that
             # exist: the scratch follows the keys in the cache, not requests x longest request
             pairs = 0
